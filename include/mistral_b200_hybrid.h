@@ -13,7 +13,7 @@
 extern "C" {
 #endif
 
-#define MBH_ABI_VERSION 2
+#define MBH_ABI_VERSION 3
 
 int mbh_abi_version(void);
 const char* mbh_last_error(void);
@@ -29,7 +29,8 @@ int mbh_rmsnorm(const void* x32, const void* w, void* y, int64_t T, int64_t D, f
  *   1  out32[M, N] += .        in-place add into the fp32 residual stream
  *   2  out[M, N/2]             rows of W interleaved (2c gate, 2c+1 up): g = min(gate, limit), u = clamp(up, -limit, limit),
  *                              out = g * sigmoid(alpha * g) * (u + 1)
- *   3  out32[M, N] = .         fp32 result (logits)
+ *   3  out32[M, N] = .         fp32 result (logits); with limit > 0: limit * tanh(. / limit)
+ *   5  out32[M, N] += alpha * .  the residual add of epilogue 1 with a fixed weight
  * Any M, N, K.  M <= 8 runs the weight-streaming kernel, larger M the tiled one (tensor cores for bf16). */
 int mbh_linear(const void* x, const void* w, const void* bias, void* out, void* out32, int64_t M, int64_t N, int64_t K, int epi, int64_t n_act,
                float limit, float alpha, int dt, void* stream);
@@ -117,19 +118,75 @@ int mbh_attn_latent_decode(const void* qa, const void* ring, const void* positio
 int mbh_latent_vup(const void* o_lat, const void* w_uv, const void* gate, int64_t g_pitch, int64_t g_off, void* out, int64_t T, int64_t H,
                    int64_t dv, int64_t kv_rank, int dt, void* stream);
 
-/* Router of a mixture of experts, fp32: s = softmax(W_r h) over n outputs, choice = s + correction (null: none); the outputs form
+/* Router of a mixture of experts, fp32: s = softmax(W_r h) over n outputs (score 0) or sigmoid of each output (score 1), choice = s + correction (null: none); the outputs form
  * `groups` equal groups of neighbours and only those of the `keep` groups with the largest choice stay eligible; the `top` largest
  * eligible choices are taken, weighted by s.  dense: fp32 [T, n] (0 where not chosen); idx int32 / wsel fp32 [T, top]. */
 int mbh_moe_route(const void* h, const void* w_router, const void* correction, void* dense, void* idx, void* wsel, int64_t T, int64_t width,
-                  int64_t n, int64_t groups, int64_t keep, int64_t top, int dt, void* stream);
+                  int64_t n, int64_t groups, int64_t keep, int64_t top, int score, int dt, void* stream);
 
 /* The chosen experts of few tokens: y32 [T, width] = sum_k wsel[t, k] * expert(idx[t, k])(h[t]); an index >= E is an identity
- * expert (output = h[t]).  w13 [E * 2 * ff, width] (gate and up rows interleaved), w2 [width, E * ff]; act: scratch [T * top, ff]. */
+ * expert (output = h[t]).  w13 [E * 2 * ff, width] (gate and up rows interleaved), w2 [width, E * ff]; act: scratch [T * top, ff].
+ * glu 0: experts silu(gate) * up.  glu 1: the weight multiplies the expert's INPUT and the unit is the clamped one of mbh_linear's
+ * epilogue 2: y32 = sum_k expert(wsel[t, k] * h[t]), g = min(w gate, limit), u = clamp(w up, -limit, limit). */
 int mbh_moe_sparse(const void* h, const void* w13, const void* w2, const void* idx, const void* wsel, void* act, void* y32, int64_t T, int64_t width,
-                   int64_t ff, int64_t E, int64_t top, int dt, void* stream);
+                   int64_t ff, int64_t E, int64_t top, int glu, float limit, float alpha, int dt, void* stream);
 
 /* y32[t, :] += (dense[t, first] + ... + dense[t, n - 1]) * h[t, :]. */
 int mbh_rows_axpy(void* y32, const void* h, const void* dense, int64_t T, int64_t n, int64_t first, int64_t D, int dt, void* stream);
+
+/* mbh_attn_bias with a sliding window and a ring that may be shorter than the sequence.  window > 0: the token at position p sees keys
+ * p - window + 1 .. p only.  own_k [T, G*d] / own_v [T, G*e] (token-major, with seqpos [B] = tokens cached before this call): keys and
+ * values of THIS call's tokens, read from there instead of the ring, so that a prompt longer than the ring finds all its keys; the ring
+ * is written after attention (mbh_kv_scatter).  Without them every visible key must be in the ring (window <= W). */
+int mbh_attn_window(const void* q, const void* cache_k, const void* cache_v, const void* bias_tab, int64_t n_tab, const void* positions,
+                    const void* q_start, const void* slots, void* out, int64_t T, int64_t B, int64_t W, int64_t H, int64_t G, int64_t d, int64_t e,
+                    float scale, int64_t n_tiles, int64_t splits, void* scratch, int64_t window, const void* own_k, const void* own_v,
+                    const void* seqpos, int dt, void* stream);
+
+/* Linear with interleaved gate/up rows and the clamped gated unit of mbh_linear's epilogue 2; gate and up of column c are multiplied by
+ * rowscale[m, c / rs_group] (fp32 [M, rs_pitch]; null: 1) BEFORE the clamps.  mbh_glu_epilogue applies the same to y[M, N] of another GEMM. */
+int mbh_linear_glu(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, float limit, float alpha, const void* rowscale,
+                   int64_t rs_pitch, int64_t rs_group, int dt, void* stream);
+int mbh_glu_epilogue(const void* y, void* out, int64_t M, int64_t N, float limit, float alpha, const void* rowscale, int64_t rs_pitch, int64_t rs_group,
+                     int dt, void* stream);
+
+/* x32[t, :] = table[tokens[t], :] * scale + pos_table[positions[t], :] (learned positions; positions int32 [T]). */
+int mbh_embed_pos(const void* tokens, const void* positions, const void* table, const void* pos_table, float scale, void* x32, int64_t T, int64_t D,
+                  int dt, void* stream);
+
+/* Splits qkv[T, H*d + G*d + G*e]; rotates the first rot_dims entries of every q and k head as interleaved pairs (2i, 2i + 1) by the angle
+ * positions[t] * freq[i] (freq: float64 [rot_dims / 2]); with unit_norm divides every rotated head by sqrt(mean(x^2) + eps).  Writes
+ * q_out [T, H*d]; k_out [T, G*d] and v_out [T, G*e] (both or neither); and, when cache_rows is given, k and v of token t into ring row
+ * cache_rows[t] (-1: not cached). */
+int mbh_rot_prep(const void* qkv, const void* freq, const void* positions, const void* cache_rows, void* q_out, void* k_out, void* v_out, void* ring_k,
+                 void* ring_v, int64_t T, int64_t H, int64_t G, int64_t d, int64_t e, int64_t rot_dims, int unit_norm, float eps, int dt, void* stream);
+
+/* ring_k[cache_rows[t]] = k[t] (Nk entries), ring_v[cache_rows[t]] = v[t] (Nv entries) for every t with cache_rows[t] >= 0. */
+int mbh_kv_scatter(const void* k, const void* v, const void* cache_rows, void* ring_k, void* ring_v, int64_t T, int64_t Nk, int64_t Nv, int dt,
+                   void* stream);
+
+/* Gated linear recurrence per head: S <- diag(a_t) S + b_t v_t^T, o_t = S^T q_t.  qab fp32 [T, 3, H*d] = q | a | b; value (t, h, c) at
+ * v[t * v_pitch + v_off + h*e + c] (storage type); state fp32 [slots, state_stride], head h's matrix [d, e + ones] at h * d * (e + ones),
+ * read (unless seqpos[b] == 0: zero) and written back; o32 fp32 [T, H * (e + ones)].  ones = 1: one more state column whose value is 1
+ * for every token (a normaliser n <- a n + b; o32 has n . q there). */
+int mbh_gated_scan(const void* qab, const void* v, int64_t v_pitch, int64_t v_off, void* state, int64_t state_stride, const void* q_start,
+                   const void* seqpos, const void* slots, void* o32, int64_t B, int64_t H, int64_t d, int64_t e, int ones, int dt, void* stream);
+
+/* HGRN2 gates from qfv [T, pitch] = silu(q) | f_pre | v: f = lower + (1 - lower) * sigmoid(f_pre); qab [T, 3, Hd] = q | f | 1 - f. */
+int mbh_hgrn2_gates(const void* qfv, const void* lower, void* qab, int64_t T, int64_t Hd, int64_t pitch, int dt, void* stream);
+
+/* mLSTM gates.  gif fp32 [T, 2H] = i_pre | f_pre; i = cap tanh(i_pre / cap), f = logsigmoid(cap tanh(f_pre / cap)); the running maximum
+ * m_t = max(f + m_(t-1), i) starts at 0 (seqpos[b] == 0) or at state[slot * state_stride + m_off + h] and is written back there.
+ * gates fp32 [T, H, 3] = exp(f + m_(t-1) - m_t), exp(i - m_t), exp(-m_t); qab [T, 3, H*d] = q * qscale | decay | exp(i - m_t) k, with
+ * q and k the first two blocks of qkvg [T, pitch]. */
+int mbh_mlstm_gates(const void* qkvg, const void* gif, void* gates, void* qab, void* state, int64_t state_stride, int64_t m_off, const void* q_start,
+                    const void* seqpos, const void* slots, int64_t T, int64_t B, int64_t H, int64_t d, int64_t pitch, float cap, float qscale, int dt,
+                    void* stream);
+
+/* After a scan: o = o32[t, h, :e] (divided by max(|o32[t, h, e]|, gates[t, h, 2]) + 1e-6 with ones = 1); y = o / sqrt(mean(o^2) + eps) * w
+ * (w [H*e] with w_per_head, else [e] shared by the heads) * sigmoid(gate[t * g_pitch + g_off + h*e + c]) (gate null: none).  y [T, H*e]. */
+int mbh_scan_post(const void* o32, const void* gates, const void* w, int w_per_head, const void* gate, int64_t g_pitch, int64_t g_off, void* y,
+                  int64_t T, int64_t H, int64_t e, int ones, float eps, int dt, void* stream);
 
 #ifdef __cplusplus
 }

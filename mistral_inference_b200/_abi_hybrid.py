@@ -13,8 +13,8 @@ import torch
 from . import _abi, build
 from ._abi import Mb200Error
 
-ABI_VERSION = 2
-EPI_STORE, EPI_RESIDUAL, EPI_GLU, EPI_F32 = 0, 1, 2, 3
+ABI_VERSION = 3
+EPI_STORE, EPI_RESIDUAL, EPI_GLU, EPI_F32, EPI_RESIDUAL_SCALED = 0, 1, 2, 3, 5
 _DT = {torch.bfloat16: 0, torch.float32: 1}
 _lib: Optional[ctypes.CDLL] = None
 
@@ -41,8 +41,18 @@ _SIGNATURES = {
     "mbh_attn_latent": (c_int, [P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, c_int, P]),
     "mbh_attn_latent_decode": (c_int, [P, P, P, P, P, I, I, I, I, I, F, I, P, c_int, P]),
     "mbh_latent_vup": (c_int, [P, P, P, I, I, P, I, I, I, I, c_int, P]),
-    "mbh_moe_route": (c_int, [P, P, P, P, P, P, I, I, I, I, I, I, c_int, P]),
-    "mbh_moe_sparse": (c_int, [P, P, P, P, P, P, P, I, I, I, I, I, c_int, P]),
+    "mbh_moe_route": (c_int, [P, P, P, P, P, P, I, I, I, I, I, I, c_int, c_int, P]),
+    "mbh_moe_sparse": (c_int, [P, P, P, P, P, P, P, I, I, I, I, I, c_int, F, F, c_int, P]),
+    "mbh_attn_window": (c_int, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, I, P, P, P, c_int, P]),
+    "mbh_linear_glu": (c_int, [P, P, P, I, I, I, F, F, P, I, I, c_int, P]),
+    "mbh_glu_epilogue": (c_int, [P, P, I, I, F, F, P, I, I, c_int, P]),
+    "mbh_embed_pos": (c_int, [P, P, P, P, F, P, I, I, c_int, P]),
+    "mbh_rot_prep": (c_int, [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, c_int, F, c_int, P]),
+    "mbh_kv_scatter": (c_int, [P, P, P, P, P, I, I, I, c_int, P]),
+    "mbh_gated_scan": (c_int, [P, P, I, I, P, I, P, P, P, P, I, I, I, I, c_int, c_int, P]),
+    "mbh_hgrn2_gates": (c_int, [P, P, P, I, I, I, c_int, P]),
+    "mbh_mlstm_gates": (c_int, [P, P, P, P, P, I, I, P, P, P, I, I, I, I, I, F, F, c_int, P]),
+    "mbh_scan_post": (c_int, [P, P, P, c_int, P, I, I, P, I, I, I, c_int, F, c_int, P]),
     "mbh_rows_axpy": (c_int, [P, P, P, I, I, I, I, c_int, P]),
 }
 
@@ -120,12 +130,13 @@ def _prompt_gemm_ok(x: torch.Tensor, M: int, N: int, K: int) -> bool:
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *, epi: int = EPI_STORE, n_act: int = 0,
            residual: Optional[torch.Tensor] = None, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
     """x [M, K] @ w [N, K]^T with the epilogues of include/mistral_b200_hybrid.h.  EPI_RESIDUAL adds into `residual` (fp32, in
-    place) and returns it; EPI_F32 returns fp32 [M, N]; EPI_GLU returns [M, N/2]."""
+    place; EPI_RESIDUAL_SCALED: times `alpha`) and returns it; EPI_F32 returns fp32 [M, N] (soft-capped at `limit` when positive);
+    EPI_GLU returns [M, N/2]."""
     M, K = x.shape
     N = w.shape[0]
     assert w.shape[1] == K and x.dtype == w.dtype
     out = out32 = None
-    if epi == EPI_RESIDUAL:
+    if epi in (EPI_RESIDUAL, EPI_RESIDUAL_SCALED):
         assert residual is not None and residual.dtype == torch.float32 and residual.shape == (M, N)
         out32 = residual
     elif epi == EPI_F32:
@@ -221,26 +232,28 @@ def linear_swiglu(x: torch.Tensor, w: torch.Tensor, rowscale: Optional[torch.Ten
     return out
 
 
-def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], groups: int, keep: int, top: int):
-    """(dense fp32 [T, n], idx int32 [T, top], wsel fp32 [T, top]) of the fp32 router."""
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], groups: int, keep: int, top: int, score: int = 0):
+    """(dense fp32 [T, n], idx int32 [T, top], wsel fp32 [T, top]) of the fp32 router; score 0: softmax, 1: sigmoid."""
     T, D = h.shape
     n = w_router.shape[0]
     dense = torch.empty(T, n, dtype=torch.float32, device=h.device)
     idx = torch.empty(T, top, dtype=torch.int32, device=h.device)
     wsel = torch.empty(T, top, dtype=torch.float32, device=h.device)
-    _check(lib().mbh_moe_route(_ptr(h), _ptr(w_router), _ptr(correction), _ptr(dense), _ptr(idx), _ptr(wsel), T, D, n, groups, keep, top,
+    _check(lib().mbh_moe_route(_ptr(h), _ptr(w_router), _ptr(correction), _ptr(dense), _ptr(idx), _ptr(wsel), T, D, n, groups, keep, top, score,
                                dt_of(h.dtype), _stream()), "mbh_moe_route")
     return dense, idx, wsel
 
 
-def moe_sparse(h: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, idx: torch.Tensor, wsel: torch.Tensor, E: int, ff: int) -> torch.Tensor:
-    """fp32 [T, width]: the weighted sum of each token's chosen experts (indices >= E: identity), streaming only their weights."""
+def moe_sparse(h: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, idx: torch.Tensor, wsel: torch.Tensor, E: int, ff: int,
+               glu: bool = False, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
+    """fp32 [T, width]: the weighted sum of each token's chosen experts (indices >= E: identity), streaming only their weights.
+    glu: clamped gated experts whose INPUT is multiplied by the routing weight."""
     T, D = h.shape
     top = idx.shape[1]
     act = torch.empty(T * top, ff, dtype=h.dtype, device=h.device)
     y32 = torch.empty(T, D, dtype=torch.float32, device=h.device)
-    _check(lib().mbh_moe_sparse(_ptr(h), _ptr(w13), _ptr(w2), _ptr(idx), _ptr(wsel), _ptr(act), _ptr(y32), T, D, ff, E, top, dt_of(h.dtype), _stream()),
-           "mbh_moe_sparse")
+    _check(lib().mbh_moe_sparse(_ptr(h), _ptr(w13), _ptr(w2), _ptr(idx), _ptr(wsel), _ptr(act), _ptr(y32), T, D, ff, E, top, int(glu), limit, alpha,
+                                dt_of(h.dtype), _stream()), "mbh_moe_sparse")
     return y32
 
 
@@ -325,4 +338,98 @@ def latent_vup(o_lat, w_uv, gate, g_pitch: int, g_off: int, H: int, dv: int, kv_
     out = torch.empty(T, H * dv, dtype=o_lat.dtype, device=o_lat.device)
     _check(lib().mbh_latent_vup(_ptr(o_lat), _ptr(w_uv), _ptr(gate), g_pitch, g_off, _ptr(out), T, H, dv, kv_rank, dt_of(o_lat.dtype), _stream()),
            "mbh_latent_vup")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ learned positions, rotary window attention
+def embed_pos(tokens: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, pos_table: torch.Tensor, scale: float) -> torch.Tensor:
+    """fp32 [T, D] = table[tokens] * scale + pos_table[positions]."""
+    T, D = tokens.shape[0], table.shape[1]
+    assert tokens.dtype == torch.long and positions.dtype == torch.int32 and pos_table.shape[1] == D and pos_table.dtype == table.dtype
+    out = torch.empty(T, D, dtype=torch.float32, device=table.device)
+    _check(lib().mbh_embed_pos(_ptr(tokens), _ptr(positions), _ptr(table), _ptr(pos_table), scale, _ptr(out), T, D, dt_of(table.dtype), _stream()),
+           "mbh_embed_pos")
+    return out
+
+
+def rot_prep(qkv, freq, positions, cache_rows, ring_k, ring_v, H: int, G: int, d: int, e: int, rot_dims: int, unit_norm: bool, eps: float, own: bool):
+    """(q [T, H*d], k [T, G*d] or None, v [T, G*e] or None): rotated (and unit-normed) queries and keys.  `own`: k and v are
+    returned token-major; `cache_rows` given: they are written into the ring rows as well."""
+    assert freq.dtype == torch.float64 and freq.numel() == rot_dims // 2
+    T = qkv.shape[0]
+    q = torch.empty(T, H * d, dtype=qkv.dtype, device=qkv.device)
+    k = torch.empty(T, G * d, dtype=qkv.dtype, device=qkv.device) if own else None
+    v = torch.empty(T, G * e, dtype=qkv.dtype, device=qkv.device) if own else None
+    _check(lib().mbh_rot_prep(_ptr(qkv), _ptr(freq), _ptr(positions), _ptr(cache_rows), _ptr(q), _ptr(k), _ptr(v), _ptr(ring_k), _ptr(ring_v), T, H, G,
+                              d, e, rot_dims, int(unit_norm), eps, dt_of(qkv.dtype), _stream()), "mbh_rot_prep")
+    return q, k, v
+
+
+def kv_scatter(k, v, cache_rows, ring_k, ring_v) -> None:
+    _check(lib().mbh_kv_scatter(_ptr(k), _ptr(v), _ptr(cache_rows), _ptr(ring_k), _ptr(ring_v), k.shape[0], k.shape[1], v.shape[1], dt_of(k.dtype),
+                                _stream()), "mbh_kv_scatter")
+
+
+def attn_window(q, cache_k, cache_v, positions, q_start, slots, out, B: int, W: int, H: int, G: int, d: int, e: int, scale: float, window: int,
+                own_k=None, own_v=None, seqpos=None, n_tiles: int = 0, splits: int = 1) -> None:
+    """`attn_bias` without a bias, with a sliding window (0: none) and, for prompts, this call's own keys and values beside the ring."""
+    scratch = torch.empty(q.shape[0] * H * splits * (2 + e), dtype=torch.float32, device=q.device) if splits > 1 and n_tiles == 0 else None
+    _check(lib().mbh_attn_window(_ptr(q), _ptr(cache_k), _ptr(cache_v), None, 0, _ptr(positions), _ptr(q_start), _ptr(slots), _ptr(out), q.shape[0], B, W,
+                                 H, G, d, e, scale, n_tiles, splits, _ptr(scratch), window, _ptr(own_k), _ptr(own_v), _ptr(seqpos), dt_of(q.dtype),
+                                 _stream()), "mbh_attn_window")
+
+
+# ------------------------------------------------------------------------------------------------ gated linear recurrences
+def gated_scan(qab, v, v_pitch: int, v_off: int, state, q_start, seqpos, slots, B: int, H: int, d: int, e: int, ones: bool) -> torch.Tensor:
+    """fp32 [T, H * (e + ones)] of S <- diag(a) S + b v^T, o = S^T q; the state rows of `slots` are read and written."""
+    assert qab.dtype == torch.float32 and state.dtype == torch.float32
+    T = qab.shape[0]
+    o = torch.empty(T, H * (e + int(ones)), dtype=torch.float32, device=qab.device)
+    _check(lib().mbh_gated_scan(_ptr(qab), _ptr(v), v_pitch, v_off, _ptr(state), state[0].numel(), _ptr(q_start), _ptr(seqpos), _ptr(slots), _ptr(o), B, H, d,
+                                e, int(ones), dt_of(v.dtype), _stream()), "mbh_gated_scan")
+    return o
+
+
+def hgrn2_gates(qfv, lower, Hd: int) -> torch.Tensor:
+    T = qfv.shape[0]
+    qab = torch.empty(T, 3, Hd, dtype=torch.float32, device=qfv.device)
+    _check(lib().mbh_hgrn2_gates(_ptr(qfv), _ptr(lower), _ptr(qab), T, Hd, qfv.shape[1], dt_of(qfv.dtype), _stream()), "mbh_hgrn2_gates")
+    return qab
+
+
+def mlstm_gates(qkvg, gif, state, m_off: int, q_start, seqpos, slots, B: int, H: int, d: int, cap: float, qscale: float):
+    """(gates fp32 [T, H, 3], qab fp32 [T, 3, H*d]); advances the running maxima kept in `state`."""
+    T = qkvg.shape[0]
+    gates = torch.empty(T, H, 3, dtype=torch.float32, device=qkvg.device)
+    qab = torch.empty(T, 3, H * d, dtype=torch.float32, device=qkvg.device)
+    _check(lib().mbh_mlstm_gates(_ptr(qkvg), _ptr(gif), _ptr(gates), _ptr(qab), _ptr(state), state[0].numel(), m_off, _ptr(q_start), _ptr(seqpos),
+                                 _ptr(slots), T, B, H, d, qkvg.shape[1], cap, qscale, dt_of(qkvg.dtype), _stream()), "mbh_mlstm_gates")
+    return gates, qab
+
+
+def scan_post(o32, gates, w, w_per_head: bool, gate, g_pitch: int, g_off: int, H: int, e: int, ones: bool, eps: float) -> torch.Tensor:
+    T = o32.shape[0]
+    y = torch.empty(T, H * e, dtype=w.dtype, device=o32.device)
+    _check(lib().mbh_scan_post(_ptr(o32), _ptr(gates), _ptr(w), int(w_per_head), _ptr(gate), g_pitch, g_off, _ptr(y), T, H, e, int(ones), eps,
+                               dt_of(w.dtype), _stream()), "mbh_scan_post")
+    return y
+
+
+def linear_glu(x: torch.Tensor, w: torch.Tensor, limit: float, alpha: float, rowscale: Optional[torch.Tensor] = None, group: int = 0) -> torch.Tensor:
+    """The clamped gated unit over interleaved gate/up rows of w [2F, K]; gate and up of column c are multiplied by
+    rowscale[m, c // group] before the clamps (experts whose input is scaled by the routing weight, run densely)."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and x.dtype == w.dtype and N % 2 == 0
+    pitch = 0
+    if rowscale is not None:
+        assert rowscale.dtype == torch.float32 and rowscale.shape[0] == M and group > 0 and (N // 2 + group - 1) // group <= rowscale.shape[1]
+        pitch = rowscale.shape[1]
+    out = torch.empty(M, N // 2, dtype=x.dtype, device=x.device)
+    if _prompt_gemm_ok(x, M, N, K):
+        y = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        _abi.linear_residual(x, w, None, y, _workspace(x.device))
+        _check(lib().mbh_glu_epilogue(_ptr(y), _ptr(out), M, N, limit, alpha, _ptr(rowscale), pitch, group, dt_of(x.dtype), _stream()), "mbh_glu_epilogue")
+        return out
+    _check(lib().mbh_linear_glu(_ptr(x), _ptr(w), _ptr(out), M, N, K, limit, alpha, _ptr(rowscale), pitch, group, dt_of(x.dtype), _stream()), "mbh_linear_glu")
     return out

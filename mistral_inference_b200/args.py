@@ -183,17 +183,108 @@ class MoeFfArgs:
         return a
 
 
+@dataclass
+class RotaryAttentionArgs:
+    """Softmax attention with rotary positions on the first `rot_dims` entries of every query and key head (interleaved pairs
+    (2i, 2i + 1), angle position * rot_base^(-2i / rot_dims) / rot_factor), optionally a unit RMS norm of every rotated head, grouped
+    key/value heads with separate key and value sizes, and optionally a sliding window of `window` positions (the token itself
+    included; None: the whole sequence)."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: Optional[int] = None
+    rot_base: float = 10000.0
+    rot_dims: int = 0          # 0: no rotation
+    rot_factor: float = 1.0    # linear scaling: every frequency divided by it
+    unit_norm: bool = True
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "RotaryAttentionArgs":
+        rot = d.get("rot") or {}
+        a = cls(heads=int(d["heads"]), kv_heads=int(d["kv_heads"]), dim=int(d["dim"]), vdim=int(d["vdim"]), scale=float(d["scale"]),
+                window=int(d["mask"]["size"]) if d.get("mask") else None, rot_base=float(rot.get("base", 10000.0)),
+                rot_dims=int(rot.get("dims", d["dim"])) if rot else 0, rot_factor=float((rot.get("scaling") or {}).get("factor", 1.0)))
+        assert a.heads % a.kv_heads == 0, "query heads must be a multiple of key/value heads"
+        assert a.rot_dims <= a.dim and a.rot_dims % 2 == 0, "the rotation covers an even number of a head's entries"
+        assert a.window is None or a.window >= 1
+        return a
+
+
+@dataclass
+class Hgrn2Args:
+    """Linear attention whose per-channel forget gate f = lower + (1 - lower) sigmoid(.) also decides what is written:
+    S <- diag(f) S + (1 - f) v^T, o = S^T q; fp32 state [heads, dim, vdim] per sequence."""
+    heads: int
+    dim: int
+    vdim: int
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "Hgrn2Args":
+        return cls(heads=int(d["heads"]), dim=int(d["dim"]), vdim=int(d["vdim"]))
+
+
+@dataclass
+class SideBySideArgs:
+    """Two mixers reading the same input, summed with fixed weights: left_scale * attention + right_scale * recurrence."""
+    left: RotaryAttentionArgs
+    right: Hgrn2Args
+    left_scale: float
+    right_scale: float
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "SideBySideArgs":
+        return cls(left=RotaryAttentionArgs.from_dict(d["left"]), right=Hgrn2Args.from_dict(d["right"]), left_scale=float(d["left_scale"]),
+                   right_scale=float(d["right_scale"]))
+
+
+@dataclass
+class MlstmArgs:
+    """Matrix memory with exponential input and forget gates (capped by gate_cap * tanh(. / gate_cap)) and a running maximum that
+    keeps them in range; fp32 state per sequence: [heads, dim, vdim] memory, [heads, dim] normaliser, [heads] maximum."""
+    heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "MlstmArgs":
+        return cls(heads=int(d["heads"]), dim=int(d["dim"]), vdim=int(d["vdim"]), gate_cap=float(d["gate_cap"]))
+
+
+@dataclass
+class ScaledInputMoeArgs:
+    """Mixture of clamped gated experts (ClampedGluArgs form) with an fp32 sigmoid router: the `top` largest scores are chosen and
+    each chosen expert runs on score * input (scores not renormalised); an optional shared expert runs for every token."""
+    ff: int
+    limit: float
+    experts: int
+    top: int
+    shared: Optional[ClampedGluArgs] = None
+    alpha: float = 1.702
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "ScaledInputMoeArgs":
+        r, sh = d["router"], d.get("shared")
+        a = cls(ff=int(d["expert"]["ff"]), limit=float(d["expert"]["limit"]), experts=int(r["experts"]), top=int(r["top"]),
+                shared=ClampedGluArgs(ff=int(sh["ff"]), limit=float(sh["limit"])) if sh else None)
+        assert 1 <= a.top <= a.experts, "top must be between 1 and the number of experts"
+        return a
+
+
 MLP_ARGS = {"dense": ClampedGluArgs, "moe": MoeFfArgs}
 
 
 @dataclass
 class LayerArgs:
     type: str                                             # a key of MIXER_ARGS
-    mixer: Union[BiasedAttentionArgs, LightningArgs, LatentAttentionArgs]
-    mlp: Union[None, ClampedGluArgs, MoeFfArgs]
+    mixer: Union[BiasedAttentionArgs, LightningArgs, LatentAttentionArgs, SideBySideArgs, MlstmArgs]
+    mlp: Union[None, ClampedGluArgs, MoeFfArgs, ScaledInputMoeArgs]
 
 
-MIXER_ARGS = {"attention": BiasedAttentionArgs, "lightning": LightningArgs, "latent_attention": LatentAttentionArgs}
+MIXER_ARGS = {"attention": BiasedAttentionArgs, "lightning": LightningArgs, "latent_attention": LatentAttentionArgs,
+              "parallel": SideBySideArgs, "mlstm": MlstmArgs, "mlstm_2": MlstmArgs}
 
 
 @dataclass
@@ -205,12 +296,15 @@ class LoopArgs:
     times: int
 
 
-# What a design fixes (not in config.json): the kind of norm, and whether each sublayer's output is normed again before it is
-# added to the residual stream.
+# What a design fixes (not in config.json): the kind of norm, whether each sublayer's output is normed again before it is added
+# to the residual stream, whether mixer and feed-forward of a layer read the same normed input (one norm per layer) and are added
+# together, whether a learned position vector is added to the embedding, and which feed-forward a kind names (default: MLP_ARGS).
 DESIGNS = {
     "Fesenex": {"norm": "rms", "post_norm": False},
     "Taruvik": {"norm": "layer", "post_norm": True},
+    "Lotazen": {"norm": "rms_scalar", "post_norm": False, "parallel_block": True, "learned_positions": True},
 }
+DESIGN_MLP_ARGS = {"Lotazen": {"moe": ScaledInputMoeArgs}}
 
 
 @dataclass
@@ -223,9 +317,13 @@ class LayeredArgs:
     norm_eps: float
     layers: List[LayerArgs]
     max_batch_size: int = 0
-    norm: str = "rms"            # "rms": weight only; "layer": mean removed, weight and bias
+    norm: str = "rms"            # "rms": weight only; "rms_scalar": one number as weight; "layer": mean removed, weight and bias
     post_norm: bool = False      # x <- x + norm_b(sublayer(norm(x))) instead of x <- x + sublayer(norm(x))
     loop: Optional[LoopArgs] = None
+    parallel_block: bool = False     # h = norm1(x); x <- x + mixer(h) + ff(h): one norm per layer, both sublayers read it
+    learned_positions: bool = False  # x = embed[token] + pos[position]; max_positions rows
+    max_positions: int = 0
+    logit_softcap: float = 0.0       # > 0: logits <- cap * tanh(logits / cap)
 
     def layer_runs(self) -> List[int]:
         """The layer index of every layer run, in order (a looped layer appears once per pass)."""
@@ -242,18 +340,19 @@ class LayeredArgs:
     @classmethod
     def from_dict(cls, d: dict) -> "LayeredArgs":
         layers = []
+        if d["architecture"] not in DESIGNS:
+            raise ValueError(f"unknown architecture {d['architecture']!r} (known: {sorted(DESIGNS)})")
+        mlp_args = {**MLP_ARGS, **DESIGN_MLP_ARGS.get(d["architecture"], {})}
         for L in d["layers"]:
             if L["type"] not in MIXER_ARGS:
                 raise ValueError(f"unknown mixer type {L['type']!r}")
             mlp = None
             if L.get("mlp") is not None:
                 kind = L["mlp"].get("kind", "dense")
-                if kind not in MLP_ARGS:
+                if kind not in mlp_args:
                     raise ValueError(f"unknown feed-forward kind {kind!r}")
-                mlp = MLP_ARGS[kind].from_dict(L["mlp"])
+                mlp = mlp_args[kind].from_dict(L["mlp"])
             layers.append(LayerArgs(type=L["type"], mixer=MIXER_ARGS[L["type"]].from_dict(L["mixer"]), mlp=mlp))
-        if d["architecture"] not in DESIGNS:
-            raise ValueError(f"unknown architecture {d['architecture']!r} (known: {sorted(DESIGNS)})")
         loop = None
         if d.get("loop"):
             lp = d["loop"]
@@ -261,4 +360,5 @@ class LayeredArgs:
             assert 0 <= loop.start < loop.stop <= len(layers) and loop.times >= 1, "loop: 0 <= start < stop <= layers, times >= 1"
         return cls(architecture=d["architecture"], vocab=int(d["vocab"]), width=int(d["width"]),
                    embedding_scale=float((d.get("embedding") or {}).get("scale", 1.0)), norm_eps=float(d["norm"]["eps"]), layers=layers,
-                   loop=loop, **DESIGNS[d["architecture"]])
+                   loop=loop, max_positions=int(d.get("max_positions", 0)), logit_softcap=float(d.get("logit_softcap") or 0.0),
+                   **DESIGNS[d["architecture"]])

@@ -39,7 +39,8 @@ def get_cache_sizes(n_layers: int, max_seq_len: int, sliding_window: SlidingWind
 @dataclass
 class LayerCacheSpec:
     """What one layer keeps per sequence.  kind "ring": keys [W, n_kv_heads, k_dim] and values [W, n_kv_heads, v_dim] in the model
-    dtype (window None = the whole sequence).  kind "state": one fp32 tensor of `state_shape`, carried from token to token."""
+    dtype (window None = the whole sequence).  kind "state": one fp32 tensor of `state_shape`, carried from token to token.  A ring
+    layer with a non-empty `state_shape` keeps both (a layer whose mixer is an attention beside a recurrence)."""
     kind: str = "ring"
     n_kv_heads: int = 0
     k_dim: int = 0
@@ -121,6 +122,8 @@ class BufferCache:
             elif sp.kind == "ring":
                 self.cache_k[i] = torch.empty((max_batch_size, cache_size, sp.n_kv_heads, sp.k_dim))
                 self.cache_v[i] = torch.empty((max_batch_size, cache_size, sp.n_kv_heads, sp.v_dim))
+                if sp.state_shape:
+                    self.cache_state[i] = torch.empty((max_batch_size, *sp.state_shape), dtype=torch.float32)
             else:
                 assert sp.kind == "state", sp.kind
                 self.cache_state[i] = torch.empty((max_batch_size, *sp.state_shape), dtype=torch.float32)

@@ -6,6 +6,8 @@
 #include "hybrid_attn_flash.cuh"
 #include "hybrid_latent.cuh"
 #include "hybrid_moe.cuh"
+#include "hybrid_rotary.cuh"
+#include "hybrid_gated_scan.cuh"
 #include "../../../include/mistral_b200_hybrid.h"
 
 #include <stdio.h>
@@ -40,6 +42,19 @@ static cudaError_t launch_lightning(const LightningArgs& a, cudaStream_t st) {
 }
 
 
+template <typename T>
+static cudaError_t launch_gated_scan(const GatedScanArgs& a, cudaStream_t st) {
+    dim3 grid(a.B * a.H, (a.e + a.ones + GS_THREADS - 1) / GS_THREADS);
+    if (a.d <= 32) gated_scan_kernel<T, 32, 16><<<grid, GS_THREADS, 0, st>>>(a);
+    else if (a.d <= 64) gated_scan_kernel<T, 64, 16><<<grid, GS_THREADS, 0, st>>>(a);
+    else gated_scan_kernel<T, 128, 8><<<grid, GS_THREADS, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+template <typename T> static void run_mlstm_gates(const MlstmGateArgs& a, int64_t B, int64_t T_, cudaStream_t st) {
+    mlstm_m_kernel<T><<<(unsigned)(B * a.H), 32, 0, st>>>(a);
+    mlstm_qab_kernel<T><<<(unsigned)T_, 128, 0, st>>>(a);
+}
 template <typename T> static void run_embed(const void* tokens, const void* table, float scale, void* x32, int64_t T_, int64_t D, cudaStream_t st) {
     embed_scale_kernel<T><<<(unsigned)T_, 128, 0, st>>>((const int64_t*)tokens, (const T*)table, scale, (float*)x32, (int)D);
 }
@@ -116,7 +131,7 @@ int mbh_rmsnorm(const void* x32, const void* w, void* y, int64_t T, int64_t D, f
 
 int mbh_linear(const void* x, const void* w, const void* bias, void* out, void* out32, int64_t M, int64_t N, int64_t K, int epi, int64_t n_act,
                float limit, float alpha, int dt, void* stream) {
-    if (epi < 0 || epi > 3) return bad("mbh_linear: unknown epilogue");  // EPI_SWIGLU: mbh_linear_swiglu
+    if ((epi < 0 || epi > 3) && epi != EPI_RESIDUAL_SCALED) return bad("mbh_linear: unknown epilogue");  // EPI_SWIGLU: mbh_linear_swiglu
     if (epi == EPI_GLU && (N & 1)) return bad("mbh_linear: the gated epilogue needs interleaved (even) rows");
     LinearArgs a{x, w, bias, out, (float*)out32, (int)M, (int)N, (int)K, epi, (int)n_act, limit, alpha};
     cudaError_t e = cudaSuccess;
@@ -126,7 +141,7 @@ int mbh_linear(const void* x, const void* w, const void* bias, void* out, void* 
 
 int mbh_linear_epilogue(const void* y, const void* bias, void* out, void* out32, int64_t M, int64_t N, int epi, int64_t n_act, float limit, float alpha,
                         int dt, void* stream) {
-    if (epi < 0 || epi > 3 || (N & 1)) return bad("mbh_linear_epilogue: unknown epilogue or odd N");
+    if (((epi < 0 || epi > 3) && epi != EPI_RESIDUAL_SCALED) || (N & 1)) return bad("mbh_linear_epilogue: unknown epilogue or odd N");
     if (M == 0) return 0;
     LinearArgs a{nullptr, nullptr, bias, out, (float*)out32, (int)M, (int)N, 0, epi, (int)n_act, limit, alpha};
     cudaStream_t st = (cudaStream_t)stream;
@@ -150,12 +165,23 @@ int mbh_attn_prep(const void* qkv, const void* qnorm, const void* knorm, const v
 int mbh_attn_bias(const void* q, const void* cache_k, const void* cache_v, const void* bias_tab, int64_t n_tab, const void* positions,
                   const void* q_start, const void* slots, void* out, int64_t T, int64_t B, int64_t W, int64_t H, int64_t G, int64_t d, int64_t e,
                   float scale, int64_t n_tiles, int64_t splits, void* scratch, int dt, void* stream) {
+    return mbh_attn_window(q, cache_k, cache_v, bias_tab, n_tab, positions, q_start, slots, out, T, B, W, H, G, d, e, scale, n_tiles, splits, scratch,
+                           0, nullptr, nullptr, nullptr, dt, stream);
+}
+
+int mbh_attn_window(const void* q, const void* cache_k, const void* cache_v, const void* bias_tab, int64_t n_tab, const void* positions,
+                    const void* q_start, const void* slots, void* out, int64_t T, int64_t B, int64_t W, int64_t H, int64_t G, int64_t d, int64_t e,
+                    float scale, int64_t n_tiles, int64_t splits, void* scratch, int64_t window, const void* own_k, const void* own_v,
+                    const void* seqpos, int dt, void* stream) {
     if (T == 0) return 0;
     if (e > 32 * AT_MAXR) return bad("mbh_attn_bias: value size above 256");
     if (H % G) return bad("mbh_attn_bias: heads must be a multiple of kv heads");
     if (splits > AT_MAX_SPLITS) return bad("mbh_attn_bias: at most 64 splits");
+    if (window < 0 || (!own_k != !own_v) || (own_k && !seqpos)) return bad("mbh_attn_window: window >= 0; own keys, own values and seqpos come together");
+    if (!own_k && window > W) return bad("mbh_attn_window: a ring shorter than the window needs the call's own keys");
     AttnArgs a{q, cache_k, cache_v, (const float*)bias_tab, (int)n_tab, (const int*)positions, (const int*)q_start, (const int*)slots, out,
-               (int)T, (int)B, (int)W, (int)H, (int)G, (int)d, (int)e, scale, (int)(splits > 1 && scratch ? splits : 1), (float*)scratch};
+               (int)T, (int)B, (int)W, (int)H, (int)G, (int)d, (int)e, scale, (int)(splits > 1 && scratch ? splits : 1), (float*)scratch, 0, 0,
+               (int)window, own_k, own_v, (const int*)seqpos};
     const size_t smem = sizeof(float) * ((size_t)d + AT_WARPS * AT_CHUNK + AT_WARPS * (2 + 32 * AT_MAXR));
     cudaStream_t st = (cudaStream_t)stream;
     // prompts in bf16: the tensor-core kernel, when the caller counted the 64-query tiles and the sizes are instantiated
@@ -314,13 +340,14 @@ int mbh_latent_vup(const void* o_lat, const void* w_uv, const void* gate, int64_
 }
 
 int mbh_moe_route(const void* h, const void* w_router, const void* correction, void* dense, void* idx, void* wsel, int64_t T, int64_t width,
-                  int64_t n, int64_t groups, int64_t keep, int64_t top, int dt, void* stream) {
+                  int64_t n, int64_t groups, int64_t keep, int64_t top, int score, int dt, void* stream) {
     if (T == 0) return 0;
     if (groups < 1 || n % groups || keep < 1 || keep > groups) return bad("mbh_moe_route: groups must divide the routed outputs, 1 <= keep <= groups");
     if (top < 1 || top > n / groups * keep) return bad("mbh_moe_route: top exceeds the eligible outputs");
     const size_t smem = sizeof(float) * (size_t)(2 * n + 2 * groups);
     if (smem > 48 * 1024) return bad("mbh_moe_route: too many routed outputs");
-    MoeRouteArgs a{h, w_router, correction, (float*)dense, (int*)idx, (float*)wsel, (int)width, (int)n, (int)groups, (int)keep, (int)top};
+    if (score != 0 && score != 1) return bad("mbh_moe_route: score is 0 (softmax) or 1 (sigmoid)");
+    MoeRouteArgs a{h, w_router, correction, (float*)dense, (int*)idx, (float*)wsel, (int)width, (int)n, (int)groups, (int)keep, (int)top, score};
     cudaStream_t st = (cudaStream_t)stream;
     DISPATCH(dt, moe_route_kernel<ST><<<(unsigned)T, MOE_ROUTE_THREADS, smem, st>>>(a));
     cudaError_t e = cudaGetLastError();
@@ -328,9 +355,9 @@ int mbh_moe_route(const void* h, const void* w_router, const void* correction, v
 }
 
 int mbh_moe_sparse(const void* h, const void* w13, const void* w2, const void* idx, const void* wsel, void* act, void* y32, int64_t T, int64_t width,
-                   int64_t ff, int64_t E, int64_t top, int dt, void* stream) {
+                   int64_t ff, int64_t E, int64_t top, int glu, float limit, float alpha, int dt, void* stream) {
     if (T == 0) return 0;
-    MoeSparseArgs a{h, w13, w2, (const int*)idx, (const float*)wsel, act, (float*)y32, (int)width, (int)ff, (int)E, (int)top};
+    MoeSparseArgs a{h, w13, w2, (const int*)idx, (const float*)wsel, act, (float*)y32, (int)width, (int)ff, (int)E, (int)top, glu, limit, alpha};
     cudaStream_t st = (cudaStream_t)stream;
     DISPATCH(dt, run_moe_sparse<ST>(a, T, st));
     cudaError_t e = cudaGetLastError();
@@ -343,6 +370,106 @@ int mbh_rows_axpy(void* y32, const void* h, const void* dense, int64_t T, int64_
     DISPATCH(dt, rows_axpy_kernel<ST><<<(unsigned)T, 128, 0, st>>>((float*)y32, (const ST*)h, (const float*)dense, (int)n, (int)first, (int)D));
     cudaError_t e = cudaGetLastError();
     return e ? fail(e, "mbh_rows_axpy") : 0;
+}
+
+int mbh_linear_glu(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, float limit, float alpha, const void* rowscale,
+                   int64_t rs_pitch, int64_t rs_group, int dt, void* stream) {
+    if (N & 1) return bad("mbh_linear_glu: the gated epilogue needs interleaved (even) rows");
+    if (rowscale && rs_group <= 0) return bad("mbh_linear_glu: rs_group must be positive");
+    LinearArgs a{x, w, nullptr, out, nullptr, (int)M, (int)N, (int)K, EPI_GLU, 0, limit, alpha, (const float*)rowscale, (int)rs_pitch, (int)rs_group};
+    cudaError_t e = cudaSuccess;
+    DISPATCH(dt, e = launch_linear<ST>(a, (cudaStream_t)stream));
+    return e ? fail(e, "mbh_linear_glu") : 0;
+}
+
+int mbh_glu_epilogue(const void* y, void* out, int64_t M, int64_t N, float limit, float alpha, const void* rowscale, int64_t rs_pitch, int64_t rs_group,
+                     int dt, void* stream) {
+    if (N & 1) return bad("mbh_glu_epilogue: odd N");
+    if (rowscale && rs_group <= 0) return bad("mbh_glu_epilogue: rs_group must be positive");
+    if (M == 0) return 0;
+    LinearArgs a{nullptr, nullptr, nullptr, out, nullptr, (int)M, (int)N, 0, EPI_GLU, 0, limit, alpha, (const float*)rowscale, (int)rs_pitch, (int)rs_group};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, run_epilogue<ST>(a, y, st));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_glu_epilogue") : 0;
+}
+
+int mbh_embed_pos(const void* tokens, const void* positions, const void* table, const void* pos_table, float scale, void* x32, int64_t T, int64_t D,
+                  int dt, void* stream) {
+    if (T == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, embed_pos_kernel<ST><<<(unsigned)T, 128, 0, st>>>((const int64_t*)tokens, (const int*)positions, (const ST*)table, (const ST*)pos_table,
+                                                                    scale, (float*)x32, (int)D));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_embed_pos") : 0;
+}
+
+int mbh_rot_prep(const void* qkv, const void* freq, const void* positions, const void* cache_rows, void* q_out, void* k_out, void* v_out, void* ring_k,
+                 void* ring_v, int64_t T, int64_t H, int64_t G, int64_t d, int64_t e, int64_t rot_dims, int unit_norm, float eps, int dt, void* stream) {
+    if (T == 0) return 0;
+    if (d > 64 * RP_MAXP) return bad("mbh_rot_prep: head size above 256");
+    if (rot_dims > d || (rot_dims & 1)) return bad("mbh_rot_prep: rot_dims must be even and at most the head size");
+    if (!k_out != !v_out) return bad("mbh_rot_prep: k_out and v_out come together");
+    if (cache_rows && (!ring_k || !ring_v)) return bad("mbh_rot_prep: ring rows without a ring");
+    RotPrepArgs a{qkv, (const double*)freq, (const int*)positions, (const int*)cache_rows, q_out, k_out, v_out, ring_k, ring_v,
+                  (int)H, (int)G, (int)d, (int)e, (int)rot_dims, unit_norm, eps};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, rot_prep_kernel<ST><<<(unsigned)T, 128, 0, st>>>(a));
+    cudaError_t err = cudaGetLastError();
+    return err ? fail(err, "mbh_rot_prep") : 0;
+}
+
+int mbh_kv_scatter(const void* k, const void* v, const void* cache_rows, void* ring_k, void* ring_v, int64_t T, int64_t Nk, int64_t Nv, int dt,
+                   void* stream) {
+    if (T == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, kv_scatter_kernel<ST><<<(unsigned)T, 128, 0, st>>>((const ST*)k, (const ST*)v, (const int*)cache_rows, (ST*)ring_k, (ST*)ring_v, (int)Nk,
+                                                                    (int)Nv));
+    cudaError_t err = cudaGetLastError();
+    return err ? fail(err, "mbh_kv_scatter") : 0;
+}
+
+int mbh_gated_scan(const void* qab, const void* v, int64_t v_pitch, int64_t v_off, void* state, int64_t state_stride, const void* q_start,
+                   const void* seqpos, const void* slots, void* o32, int64_t B, int64_t H, int64_t d, int64_t e, int ones, int dt, void* stream) {
+    if (B == 0) return 0;
+    if (d > 128) return bad("mbh_gated_scan: key size above 128");
+    GatedScanArgs a{(const float*)qab, v, (int)v_pitch, (int)v_off, (float*)state, (int)state_stride, (const int*)q_start, (const int*)seqpos,
+                    (const int*)slots, (float*)o32, (int)B, (int)H, (int)d, (int)e, ones ? 1 : 0};
+    cudaError_t err = cudaSuccess;
+    DISPATCH(dt, err = launch_gated_scan<ST>(a, (cudaStream_t)stream));
+    return err ? fail(err, "mbh_gated_scan") : 0;
+}
+
+int mbh_hgrn2_gates(const void* qfv, const void* lower, void* qab, int64_t T, int64_t Hd, int64_t pitch, int dt, void* stream) {
+    if (T == 0) return 0;
+    Hgrn2GateArgs a{qfv, lower, (float*)qab, (int)Hd, (int)pitch};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, hgrn2_gates_kernel<ST><<<(unsigned)T, 128, 0, st>>>(a));
+    cudaError_t err = cudaGetLastError();
+    return err ? fail(err, "mbh_hgrn2_gates") : 0;
+}
+
+int mbh_mlstm_gates(const void* qkvg, const void* gif, void* gates, void* qab, void* state, int64_t state_stride, int64_t m_off, const void* q_start,
+                    const void* seqpos, const void* slots, int64_t T, int64_t B, int64_t H, int64_t d, int64_t pitch, float cap, float qscale, int dt,
+                    void* stream) {
+    if (T == 0) return 0;
+    MlstmGateArgs a{qkvg, (const float*)gif, (float*)gates, (float*)qab, (float*)state, (int)state_stride, (int)m_off, (const int*)q_start, (const int*)seqpos,
+                    (const int*)slots, (int)H, (int)d, (int)pitch, cap, qscale};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, run_mlstm_gates<ST>(a, B, T, st));
+    cudaError_t err = cudaGetLastError();
+    return err ? fail(err, "mbh_mlstm_gates") : 0;
+}
+
+int mbh_scan_post(const void* o32, const void* gates, const void* w, int w_per_head, const void* gate, int64_t g_pitch, int64_t g_off, void* y,
+                  int64_t T, int64_t H, int64_t e, int ones, float eps, int dt, void* stream) {
+    if (T == 0) return 0;
+    if (ones && !gates) return bad("mbh_scan_post: a normaliser column needs the gates");
+    ScanPostArgs a{(const float*)o32, (const float*)gates, w, w_per_head, gate, (int)g_pitch, (int)g_off, y, (int)H, (int)e, ones ? 1 : 0, eps};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, scan_post_kernel<ST><<<(unsigned)T, 128, 0, st>>>(a));
+    cudaError_t err = cudaGetLastError();
+    return err ? fail(err, "mbh_scan_post") : 0;
 }
 
 }  // extern "C"

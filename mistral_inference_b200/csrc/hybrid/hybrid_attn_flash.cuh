@@ -64,23 +64,30 @@ __global__ void __launch_bounds__(128) attn_bias_flash_kernel(AttnArgs a) {
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     const size_t base = (size_t)a.slots[b] * a.W;
     const size_t kstride = (size_t)a.G * D, vstride = (size_t)a.G * E;
-    const bf16* K = static_cast<const bf16*>(a.cache_k) + base * kstride + (size_t)g * D;
-    const bf16* V = static_cast<const bf16*>(a.cache_v) + base * vstride + (size_t)g * E;
+    const int own_from = a.own_k ? a.seqpos[b] : 0x7fffffff;
+    const size_t own_row = a.own_k ? (size_t)a.q_start[b] : 0;
+    const KeySource<bf16> Ksrc{static_cast<const bf16*>(a.cache_k) + base * kstride + (size_t)g * D,
+                               static_cast<const bf16*>(a.own_k) + own_row * kstride + (size_t)g * D, kstride, kstride, a.W, own_from};
+    const KeySource<bf16> Vsrc{static_cast<const bf16*>(a.cache_v) + base * vstride + (size_t)g * E,
+                               static_cast<const bf16*>(a.own_v) + own_row * vstride + (size_t)g * E, vstride, vstride, a.W, own_from};
+    // sliding window: the first key any row of this tile sees; key tiles below it are skipped
+    const int j_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
+    const int w0 = a.window > 0 ? a.window : 0x40000000;  // row at position p sees keys j with p - j < w0
     const float* bias = a.bias_tab ? a.bias_tab + h : nullptr;  // null: no bias
     const int last_tab = a.n_tab - 1;
 
-    for (int j0 = 0; j0 <= pos_last; j0 += FA_BK) {
+    for (int j0 = (j_lo / FA_BK) * FA_BK; j0 <= pos_last; j0 += FA_BK) {
         __syncthreads();
         for (int c = threadIdx.x; c < FA_BK * (D / 8); c += 128) {
             const int r = c / (D / 8), kc = (c % (D / 8)) * 8, j = j0 + r;
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (j <= pos_last) v = *reinterpret_cast<const uint4*>(K + (size_t)(j % a.W) * kstride + kc);
+            if (j <= pos_last && j >= j_lo) v = *reinterpret_cast<const uint4*>(Ksrc.row(j) + kc);
             *reinterpret_cast<uint4*>(&Ks[r][kc]) = v;
         }
         for (int c = threadIdx.x; c < FA_BK * (E / 8); c += 128) {
             const int r = c % FA_BK, ec = (c / FA_BK) * 8, j = j0 + r;
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (j <= pos_last) v = *reinterpret_cast<const uint4*>(V + (size_t)(j % a.W) * vstride + ec);
+            if (j <= pos_last && j >= j_lo) v = *reinterpret_cast<const uint4*>(Vsrc.row(j) + ec);
             const bf16* pv = reinterpret_cast<const bf16*>(&v);
 #pragma unroll
             for (int i = 0; i < 8; ++i) Vt[ec + i][r] = pv[i];
@@ -104,8 +111,8 @@ __global__ void __launch_bounds__(128) attn_bias_flash_kernel(AttnArgs a) {
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const int j = j0 + nt * 8 + tig * 2 + c;
-                const float x0 = (j <= p0) ? s[nt][c] * a.scale + (bias ? bias[(size_t)min(p0 - j, last_tab) * a.H] : 0.f) : -INFINITY;
-                const float x1 = (j <= p1) ? s[nt][2 + c] * a.scale + (bias ? bias[(size_t)min(p1 - j, last_tab) * a.H] : 0.f) : -INFINITY;
+                const float x0 = (j <= p0 && p0 - j < w0) ? s[nt][c] * a.scale + (bias ? bias[(size_t)min(p0 - j, last_tab) * a.H] : 0.f) : -INFINITY;
+                const float x1 = (j <= p1 && p1 - j < w0) ? s[nt][2 + c] * a.scale + (bias ? bias[(size_t)min(p1 - j, last_tab) * a.H] : 0.f) : -INFINITY;
                 s[nt][c] = x0; s[nt][2 + c] = x1;
                 mx0 = fmaxf(mx0, x0); mx1 = fmaxf(mx1, x1);
             }

@@ -1,0 +1,225 @@
+// Linear attention with data-dependent gates: one scan kernel for every recurrence of the form
+//
+//     S_t = diag(a_t) S_(t-1) + b_t v_t^T,    o_t = S_t^T q_t          per head, S [d, e] fp32, carried in the cache
+//
+// and the small kernels that turn a layer's projections into (q, a, b) and its raw output into the next Linear's input.
+//
+//   gated_scan       the recurrence; with `ones` the state has one more column whose value is 1 for every token, which carries the
+//                    normaliser n_t = a_t n_(t-1) + b_t, and o has its n_t . q_t in that column
+//   hgrn2_gates      f = l + (1 - l) sigmoid(f_pre): a = f, b = 1 - f (the forget gate also decides what is written)
+//   mlstm_m / mlstm_qab   exponential input and forget gates kept in range by a running maximum m (m_0 = 0):
+//                    i = cap tanh(i_pre / cap), f = logsigmoid(cap tanh(f_pre / cap)), m_t = max(f + m_(t-1), i),
+//                    a = exp(f + m_(t-1) - m_t) (one number per head), b = exp(i - m_t) k, q scaled; also exp(-m_t) per token
+//   scan_post        o / (max(|n . q|, exp(-m)) + 1e-6) when there is a normaliser; every head divided by its root mean square;
+//                    times a weight (per head column, or one set shared by the heads) and an optional sigmoid gate
+//
+// Everything here is fp32 except the projections that are read and the activations that are written.
+#pragma once
+#include "hybrid_common.cuh"
+
+namespace mbh {
+
+struct GatedScanArgs {
+    const float* qab;      // [T, 3, H*d]: q | a | b
+    const void* v;         // storage type: value (t, h, c) at v[t * v_pitch + v_off + h*e + c]
+    int v_pitch, v_off;
+    float* state;          // [slots, state_stride]; head h's matrix [d, e + ones] starts at h * d * (e + ones)
+    int state_stride;
+    const int* q_start;    // [B + 1]
+    const int* seqpos;     // [B] tokens before this call (0: the state starts at zero)
+    const int* slots;      // [B]
+    float* o;              // [T, H * (e + ones)]
+    int B, H, d, e, ones;
+};
+
+constexpr int GS_THREADS = 128;
+
+// One CTA per (sequence, head, block of GS_THREADS state columns); thread c owns column c of the state in DMAX registers.
+// q, a, b of GS_TB tokens at a time go through shared memory, the next tile is fetched into registers meanwhile (fewer tokens
+// per tile at the largest key size, where the state alone takes 128 registers).
+template <typename T, int DMAX, int GS_TB>
+__global__ void __launch_bounds__(GS_THREADS) gated_scan_kernel(GatedScanArgs p) {
+    constexpr int R = 3 * GS_TB * DMAX / GS_THREADS;
+    __shared__ __align__(16) float qs[GS_TB][DMAX], as[GS_TB][DMAX], bs[GS_TB][DMAX];
+    const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
+    const int c = blockIdx.y * GS_THREADS + threadIdx.x;
+    const int ec = p.e + p.ones;
+    const bool live = c < ec, is_one = c >= p.e;
+    const int t0 = p.q_start[b], t1 = p.q_start[b + 1];
+    const int Hd = p.H * p.d;
+    float* st = p.state + (size_t)p.slots[b] * p.state_stride + (size_t)h * p.d * ec;
+    float S[DMAX], pre[R];
+    const bool fresh = p.seqpos[b] == 0;
+#pragma unroll
+    for (int i = 0; i < DMAX; ++i) S[i] = (live && !fresh && i < p.d) ? st[(size_t)i * ec + c] : 0.f;
+
+    auto fetch = [&](int tb) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int idx = threadIdx.x + r * GS_THREADS;
+            const int tt = idx / (3 * DMAX), rem = idx % (3 * DMAX), which = rem / DMAX, i = rem % DMAX;
+            const bool ok = tb + tt < t1 && i < p.d;
+            pre[r] = ok ? p.qab[((size_t)(tb + tt) * 3 + which) * Hd + h * p.d + i] : 0.f;
+        }
+    };
+    fetch(t0);
+    const T* vcol = static_cast<const T*>(p.v) + p.v_off + h * p.e + (is_one ? 0 : c);
+    for (int tb = t0; tb < t1; tb += GS_TB) {
+        const int nt = min(GS_TB, t1 - tb);
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int idx = threadIdx.x + r * GS_THREADS;
+            const int tt = idx / (3 * DMAX), rem = idx % (3 * DMAX), which = rem / DMAX, i = rem % DMAX;
+            (which == 0 ? qs : which == 1 ? as : bs)[tt][i] = pre[r];
+        }
+        __syncthreads();
+        if (tb + GS_TB < t1) fetch(tb + GS_TB);
+        if (live) {
+            float vn = is_one ? 1.f : to_f(vcol[(size_t)tb * p.v_pitch]);
+            for (int tt = 0; tt < nt; ++tt) {
+                const float v = vn;
+                if (!is_one && tt + 1 < nt) vn = to_f(vcol[(size_t)(tb + tt + 1) * p.v_pitch]);
+                float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DMAX; i += 4) {
+                    const float4 a4 = *reinterpret_cast<const float4*>(&as[tt][i]);
+                    const float4 b4 = *reinterpret_cast<const float4*>(&bs[tt][i]);
+                    const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][i]);
+                    S[i] = fmaf(a4.x, S[i], b4.x * v);         o0 = fmaf(S[i], q4.x, o0);
+                    S[i + 1] = fmaf(a4.y, S[i + 1], b4.y * v); o1 = fmaf(S[i + 1], q4.y, o1);
+                    S[i + 2] = fmaf(a4.z, S[i + 2], b4.z * v); o2 = fmaf(S[i + 2], q4.z, o2);
+                    S[i + 3] = fmaf(a4.w, S[i + 3], b4.w * v); o3 = fmaf(S[i + 3], q4.w, o3);
+                }
+                p.o[(size_t)(tb + tt) * p.H * ec + h * ec + c] = (o0 + o1) + (o2 + o3);
+            }
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DMAX; ++i)
+            if (i < p.d) st[(size_t)i * ec + c] = S[i];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ HGRN2 gates
+struct Hgrn2GateArgs {
+    const void* qfv;     // [T, 2*H*d + H*e]: silu(q) | f_pre (bias added) | v
+    const void* lower;   // [H*d] lower bound of the forget gate
+    float* qab;          // [T, 3, H*d]
+    int Hd, pitch;
+};
+
+template <typename T>
+__global__ void hgrn2_gates_kernel(Hgrn2GateArgs p) {
+    const int t = blockIdx.x;
+    const T* row = static_cast<const T*>(p.qfv) + (size_t)t * p.pitch;
+    float* out = p.qab + (size_t)t * 3 * p.Hd;
+    for (int j = threadIdx.x; j < p.Hd; j += blockDim.x) {
+        const float l = to_f(static_cast<const T*>(p.lower)[j]);
+        const float f = l + (1.f - l) * sigmoid_exact(to_f(row[p.Hd + j]));
+        out[j] = to_f(row[j]);
+        out[p.Hd + j] = f;
+        out[2 * p.Hd + j] = 1.f - f;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ mLSTM gates
+struct MlstmGateArgs {
+    const void* qkvg;    // [T, pitch]: q | k | v | g
+    const float* gif;    // [T, 2H] fp32: i_pre | f_pre (bias added)
+    float* gates;        // [T, H, 3]: a (decay), s (input scale), exp(-m_t)
+    float* qab;          // [T, 3, H*d]
+    float* state;        // m of head h of a sequence at state[slot * state_stride + m_off + h]
+    int state_stride, m_off;
+    const int* q_start; const int* seqpos; const int* slots;
+    int H, d, pitch;
+    float cap, qscale;
+};
+
+__device__ __forceinline__ float logsigmoid_exact(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+// One warp per (sequence, head): lanes take 32 tokens' gates at a time, the running maximum goes through them in order.
+template <typename T>
+__global__ void __launch_bounds__(32) mlstm_m_kernel(MlstmGateArgs p) {
+    const int b = blockIdx.x / p.H, h = blockIdx.x % p.H, lane = threadIdx.x;
+    const int t0 = p.q_start[b], t1 = p.q_start[b + 1];
+    float* mst = p.state + (size_t)p.slots[b] * p.state_stride + p.m_off + h;
+    float m = p.seqpos[b] == 0 ? 0.f : *mst;
+    const float* G = p.gif;
+    for (int tb = t0; tb < t1; tb += 32) {
+        const int t = tb + lane;
+        float ig = 0.f, fg = 0.f;
+        if (t < t1) {
+            ig = p.cap * tanhf(G[(size_t)t * 2 * p.H + h] / p.cap);
+            fg = logsigmoid_exact(p.cap * tanhf(G[(size_t)t * 2 * p.H + p.H + h] / p.cap));
+        }
+        float m_prev = 0.f, m_mine = 0.f;
+        const int nt = min(32, t1 - tb);
+        for (int s = 0; s < nt; ++s) {
+            const float fs = __shfl_sync(0xffffffffu, fg, s), is = __shfl_sync(0xffffffffu, ig, s);
+            const float mn = fmaxf(fs + m, is);
+            if (lane == s) { m_prev = m; m_mine = mn; }
+            m = mn;
+        }
+        if (t < t1) {
+            float* g = p.gates + ((size_t)t * p.H + h) * 3;
+            g[0] = expf(fg + m_prev - m_mine);
+            g[1] = expf(ig - m_mine);
+            g[2] = expf(-m_mine);
+        }
+    }
+    if (lane == 0) *mst = m;
+}
+
+template <typename T>
+__global__ void mlstm_qab_kernel(MlstmGateArgs p) {
+    const int t = blockIdx.x, Hd = p.H * p.d;
+    const T* row = static_cast<const T*>(p.qkvg) + (size_t)t * p.pitch;
+    float* out = p.qab + (size_t)t * 3 * Hd;
+    for (int j = threadIdx.x; j < Hd; j += blockDim.x) {
+        const float* g = p.gates + ((size_t)t * p.H + j / p.d) * 3;
+        out[j] = to_f(row[j]) * p.qscale;
+        out[Hd + j] = g[0];
+        out[2 * Hd + j] = g[1] * to_f(row[Hd + j]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ after the scan
+struct ScanPostArgs {
+    const float* o;        // [T, H * (e + ones)]
+    const float* gates;    // [T, H, 3] (exp(-m_t) in entry 2) with `ones`, else null
+    const void* w;         // weight: [H*e] (w_per_head) or [e] shared by the heads
+    int w_per_head;
+    const void* gate;      // sigmoid gate at gate[t * g_pitch + g_off + h*e + c], or null
+    int g_pitch, g_off;
+    void* y;               // [T, H*e]
+    int H, e, ones;
+    float eps;
+};
+
+// one CTA per token, a warp per head
+template <typename T>
+__global__ void __launch_bounds__(128) scan_post_kernel(ScanPostArgs p) {
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int ec = p.e + p.ones;
+    for (int h = warp; h < p.H; h += nw) {
+        const float* o = p.o + ((size_t)t * p.H + h) * ec;
+        float den = 1.f;
+        if (p.ones) den = fmaxf(fabsf(o[p.e]), p.gates[((size_t)t * p.H + h) * 3 + 2]) + 1e-6f;
+        float ss = 0.f;
+        for (int c = lane; c < p.e; c += 32) { const float v = o[c] / den; ss = fmaf(v, v, ss); }
+        ss = warp_sum(ss);
+        const float inv = 1.f / sqrtf(ss / (float)p.e + p.eps);
+        const T* w = static_cast<const T*>(p.w) + (p.w_per_head ? h * p.e : 0);
+        const T* g = p.gate ? static_cast<const T*>(p.gate) + (size_t)t * p.g_pitch + p.g_off + h * p.e : nullptr;
+        T* y = static_cast<T*>(p.y) + ((size_t)t * p.H + h) * p.e;
+        for (int c = lane; c < p.e; c += 32) {
+            float v = o[c] / den * inv * to_f(w[c]);
+            if (g) v *= sigmoid_exact(to_f(g[c]));
+            y[c] = from_f<T>(v);
+        }
+    }
+}
+
+}  // namespace mbh

@@ -3,8 +3,11 @@
 //   EPI_STORE     out[M, N]    = act(acc + b)   act = SiLU on columns < n_act, identity elsewhere
 //   EPI_RESIDUAL  resid[M, N] += acc + b        fp32 residual stream, in place
 //   EPI_GLU       out[M, N/2]: rows of W interleaved (2c = gate, 2c + 1 = up):
-//                 g = min(gate, limit), u = clamp(up, +-limit), out = g * sigmoid(alpha * g) * (u + 1)
-//   EPI_F32       out32[M, N]  = acc + b        (logits)
+//                 g = min(gate, limit), u = clamp(up, +-limit), out = g * sigmoid(alpha * g) * (u + 1); with rowscale (as for
+//                 EPI_SWIGLU) gate and up are multiplied by rowscale[m, c / rs_group] BEFORE the clamps: experts whose INPUT is
+//                 scaled by the routing weight, run densely (weight 0 gives exactly 0)
+//   EPI_F32       out32[M, N]  = acc + b        (logits); with limit > 0: limit * tanh((acc + b) / limit), a soft cap
+//   EPI_RESIDUAL_SCALED  resid[M, N] += alpha * (acc + b)    (one of several sublayers that are summed with fixed weights)
 //   EPI_SWIGLU    out[M, N/2]: interleaved rows as for EPI_GLU: out = silu(gate) * up * rowscale[m, c / rs_group]
 //                 (rowscale fp32 [M, rs_pitch] or null: a mixture of experts run densely, every expert's hidden units scaled by
 //                 the token's routing weight, 0 for an expert that the token did not choose)
@@ -21,7 +24,7 @@
 
 namespace mbh {
 
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GLU = 2, EPI_F32 = 3, EPI_SWIGLU = 4 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GLU = 2, EPI_F32 = 3, EPI_SWIGLU = 4, EPI_RESIDUAL_SCALED = 5 };
 
 struct LinearArgs {
     const void* x; const void* w; const void* bias;
@@ -50,8 +53,14 @@ __device__ __forceinline__ void epilogue_pair(const LinearArgs& a, int m, int n,
         o[0] += v0;
         if (has1) o[1] += v1;
         break; }
+    case EPI_RESIDUAL_SCALED: {
+        float* o = a.out32 + (size_t)m * a.N + n;
+        o[0] += a.alpha * v0;
+        if (has1) o[1] += a.alpha * v1;
+        break; }
     case EPI_GLU: {
         if (!has1) break;
+        if (a.rowscale) { const float rs = a.rowscale[(size_t)m * a.rs_pitch + (n >> 1) / a.rs_group]; v0 *= rs; v1 *= rs; }
         float g = fminf(v0, a.limit), u = fminf(fmaxf(v1, -a.limit), a.limit);
         static_cast<T*>(a.out)[(size_t)m * (a.N >> 1) + (n >> 1)] = from_f<T>(g * sigmoid_exact(a.alpha * g) * (u + 1.f));
         break; }
@@ -64,6 +73,7 @@ __device__ __forceinline__ void epilogue_pair(const LinearArgs& a, int m, int n,
         break; }
     default: {
         float* o = a.out32 + (size_t)m * a.N + n;
+        if (a.limit > 0.f) { v0 = a.limit * tanhf(v0 / a.limit); v1 = a.limit * tanhf(v1 / a.limit); }
         o[0] = v0;
         if (has1) o[1] = v1;
         break; }

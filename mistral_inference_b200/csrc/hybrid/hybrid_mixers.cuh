@@ -127,6 +127,20 @@ struct AttnArgs {
     float* scratch;         // [T*H, splits, 2 + e] fp32
     int k_pitch, v_pitch;   // elements per ring row of keys / values; 0: G*d / G*e.  (A latent ring is one row per token that both
                             // pointers address: its first e entries are the value.)  bias_tab may be null: no bias.
+    int window;             // > 0: a token at position p sees keys p - window + 1 .. p only (sliding window); 0: every key up to p
+    const void* own_k; const void* own_v;  // prompts over a ring shorter than the sequence: keys / values of THIS call's tokens, token-major
+                            // [T, G*d] / [T, G*e]; key j >= seqpos[b] is row q_start[b] + j - seqpos[b] there, older keys are in the ring
+                            // (which this call's tokens are written to only after attention).  null: every key is in the ring.
+    const int* seqpos;      // [B] tokens cached before this call (with own_k)
+};
+
+// where key / value j of a sequence lives: this call's own rows, or the ring
+template <typename T>
+struct KeySource {
+    const T* ring; const T* own; size_t ring_pitch, own_pitch; int W, own_from;
+    __device__ __forceinline__ const T* row(int j) const {
+        return j >= own_from ? own + (size_t)(j - own_from) * own_pitch : ring + (size_t)(j % W) * ring_pitch;
+    }
 };
 
 constexpr int AT_WARPS = 4, AT_CHUNK = 128, AT_MAXR = 8, AT_MAXR_WIDE = 16;  // e <= 32 * MAXR
@@ -150,20 +164,26 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
     __syncthreads();
     const size_t base = (size_t)a.slots[b] * a.W;
     const size_t ks = a.k_pitch ? (size_t)a.k_pitch : (size_t)a.G * a.d, vs = a.v_pitch ? (size_t)a.v_pitch : (size_t)a.G * a.e;
-    const T* K = static_cast<const T*>(a.cache_k) + base * ks + (size_t)g * a.d;
-    const T* Vp = static_cast<const T*>(a.cache_v) + base * vs + (size_t)g * a.e;
+    const int own_from = a.own_k ? a.seqpos[b] : 0x7fffffff;
+    const size_t own_row = a.own_k ? (size_t)a.q_start[b] : 0;
+    const KeySource<T> Ksrc{static_cast<const T*>(a.cache_k) + base * ks + (size_t)g * a.d,
+                            static_cast<const T*>(a.own_k) + own_row * a.G * a.d + (size_t)g * a.d, ks, (size_t)a.G * a.d, a.W, own_from};
+    const KeySource<T> Vsrc{static_cast<const T*>(a.cache_v) + base * vs + (size_t)g * a.e,
+                            static_cast<const T*>(a.own_v) + own_row * a.G * a.e + (size_t)g * a.e, vs, (size_t)a.G * a.e, a.W, own_from};
     constexpr int V = Vec<T>::N;
-    const bool vec_ok = (a.d % V == 0) && (ks % V == 0) && (reinterpret_cast<uintptr_t>(a.cache_k) % 16 == 0);
+    const bool vec_ok = (a.d % V == 0) && (ks % V == 0) && (reinterpret_cast<uintptr_t>(a.cache_k) % 16 == 0)
+                        && (!a.own_k || reinterpret_cast<uintptr_t>(a.own_k) % 16 == 0);
+    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;  // first visible key
     float m = -INFINITY, l = 0.f, acc[MAXR];
 #pragma unroll
     for (int r = 0; r < MAXR; ++r) acc[r] = 0.f;
     const int cpl = (a.e + 31) / 32;  // value columns per lane: lane * cpl .. + cpl - 1
-    for (int c0 = (blockIdx.y * AT_WARPS + warp) * AT_CHUNK; c0 < n; c0 += a.splits * AT_WARPS * AT_CHUNK) {
+    for (int c0 = lo + (blockIdx.y * AT_WARPS + warp) * AT_CHUNK; c0 < n; c0 += a.splits * AT_WARPS * AT_CHUNK) {
         const int cn = min(AT_CHUNK, n - c0);
         float cmax = -INFINITY;
         for (int jj = lane; jj < cn; jj += 32) {
             const int j = c0 + jj;
-            const T* kr = K + (size_t)(j % a.W) * ks;
+            const T* kr = Ksrc.row(j);
             float s = 0.f;
             if (vec_ok) {
                 for (int i = 0; i < a.d; i += V) {
@@ -194,13 +214,13 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
 #pragma unroll
         for (int r = 0; r < MAXR; ++r) acc[r] *= corr;
         {
-            const T* vp = Vp + lane * cpl;
+            const int vo = lane * cpl;
             int jj = 0;
             for (; jj + 4 <= cn; jj += 4) {
-                const T* r0 = vp + (size_t)((c0 + jj) % a.W) * vs;
-                const T* r1 = vp + (size_t)((c0 + jj + 1) % a.W) * vs;
-                const T* r2 = vp + (size_t)((c0 + jj + 2) % a.W) * vs;
-                const T* r3 = vp + (size_t)((c0 + jj + 3) % a.W) * vs;
+                const T* r0 = Vsrc.row(c0 + jj) + vo;
+                const T* r1 = Vsrc.row(c0 + jj + 1) + vo;
+                const T* r2 = Vsrc.row(c0 + jj + 2) + vo;
+                const T* r3 = Vsrc.row(c0 + jj + 3) + vo;
                 const float w0 = sc[jj], w1 = sc[jj + 1], w2 = sc[jj + 2], w3 = sc[jj + 3];
 #pragma unroll
                 for (int r = 0; r < MAXR; ++r)
@@ -208,7 +228,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
                         acc[r] += w0 * to_f(r0[r]) + w1 * to_f(r1[r]) + w2 * to_f(r2[r]) + w3 * to_f(r3[r]);
             }
             for (; jj < cn; ++jj) {
-                const T* r0 = vp + (size_t)((c0 + jj) % a.W) * vs;
+                const T* r0 = Vsrc.row(c0 + jj) + vo;
                 const float w0 = sc[jj];
 #pragma unroll
                 for (int r = 0; r < MAXR; ++r)

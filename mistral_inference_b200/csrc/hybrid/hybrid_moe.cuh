@@ -25,6 +25,7 @@ struct MoeRouteArgs {
     int* idx;                 // [T, top]
     float* wsel;              // [T, top]
     int width, n, groups, keep, top;
+    int score;                // 0: softmax over the outputs; 1: sigmoid of each output
 };
 
 // (value, index) argmax over a warp; the lower index wins a tie
@@ -75,12 +76,17 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(MoeRouteAr
     }
     __syncthreads();
     if (warp != 0) return;
-    float mx = -INFINITY;
-    for (int e = lane; e < a.n; e += 32) mx = fmaxf(mx, z[e]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < a.n; e += 32) { const float p = expf(z[e] - mx); z[e] = p; sum += p; }
-    sum = warp_sum(sum);
+    float sum = 1.f;
+    if (a.score == 1) {
+        for (int e = lane; e < a.n; e += 32) z[e] = sigmoid_exact(z[e]);
+    } else {
+        float mx = -INFINITY;
+        for (int e = lane; e < a.n; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        sum = 0.f;
+        for (int e = lane; e < a.n; e += 32) { const float p = expf(z[e] - mx); z[e] = p; sum += p; }
+        sum = warp_sum(sum);
+    }
     const T* corr = static_cast<const T*>(a.correction);
     for (int e = lane; e < a.n; e += 32) {
         const float s = z[e] / sum;
@@ -136,6 +142,8 @@ struct MoeSparseArgs {
     void* act;                // [T * top, ff]
     float* y32;               // [T, width]
     int width, ff, E, top;
+    int glu;                  // 0: silu(gate) * up, the routing weight multiplies the expert's OUTPUT; 1: the weight multiplies the
+    float limit, alpha;       //    expert's INPUT: g = min(w gate, limit), u = clamp(w up, +-limit), act = g sigmoid(alpha g) (u + 1)
 };
 
 constexpr int MOE_WARPS = 8;
@@ -149,8 +157,18 @@ __global__ void __launch_bounds__(MOE_WARPS * 32) moe_gateup_sparse_kernel(MoeSp
     if (c >= a.ff) return;
     const T* h = static_cast<const T*>(a.h) + (size_t)t * a.width;
     const T* wg = static_cast<const T*>(a.w13) + ((size_t)e * a.ff + c) * 2 * a.width;
-    const float g = rnd<T>(warp_dot<T>(wg, h, a.width, lane)), u = rnd<T>(warp_dot<T>(wg + a.width, h, a.width, lane));
-    if (lane == 0) static_cast<T*>(a.act)[(size_t)slot * a.ff + c] = from_f<T>(g * sigmoid_exact(g) * u);
+    float g = rnd<T>(warp_dot<T>(wg, h, a.width, lane)), u = rnd<T>(warp_dot<T>(wg + a.width, h, a.width, lane));
+    if (lane != 0) return;
+    float act;
+    if (a.glu) {
+        const float w = a.wsel[slot];
+        g = fminf(g * w, a.limit);
+        u = fminf(fmaxf(u * w, -a.limit), a.limit);
+        act = g * sigmoid_exact(a.alpha * g) * (u + 1.f);
+    } else {
+        act = g * sigmoid_exact(g) * u;
+    }
+    static_cast<T*>(a.act)[(size_t)slot * a.ff + c] = from_f<T>(act);
 }
 
 // grid (ceil(width / MOE_WARPS), T): a warp per output column, summing the token's chosen experts in slot order
@@ -162,7 +180,7 @@ __global__ void __launch_bounds__(MOE_WARPS * 32) moe_down_sparse_kernel(MoeSpar
     float acc = 0.f;
     for (int k = 0; k < a.top; ++k) {
         const int slot = t * a.top + k, e = a.idx[slot];
-        const float w = a.wsel[slot];
+        const float w = a.glu ? 1.f : a.wsel[slot];
         if (e >= a.E) acc += w * to_f(static_cast<const T*>(a.h)[(size_t)t * a.width + n]);
         else acc += w * rnd<T>(warp_dot<T>(wrow + (size_t)e * a.ff, static_cast<const T*>(a.act) + (size_t)slot * a.ff, a.ff, lane));
     }

@@ -39,8 +39,9 @@ class LayeredTransformer(nn.Module):
             else:
                 mixer = MIXERS[L.type](args.width, L.mixer, args.norm_eps)
             mlp = FEED_FORWARDS[type(L.mlp)](args.width, L.mlp) if L.mlp is not None else None
-            blocks.append(LayeredBlock(args.width, args.norm_eps, mixer, mlp, norm=args.norm, post_norm=args.post_norm))
+            blocks.append(LayeredBlock(args.width, args.norm_eps, mixer, mlp, norm=args.norm, post_norm=args.post_norm, parallel=args.parallel_block))
         self.layers = nn.ModuleList(blocks)
+        self.pos = nn.Parameter(torch.empty(args.max_positions, args.width), requires_grad=False) if args.learned_positions else None
         self.final_norm = Norm(args.width, args.norm_eps, args.norm)
         self.head = nn.Parameter(torch.empty(args.vocab, args.width), requires_grad=False)
         self.last_argmax: Optional[torch.Tensor] = None
@@ -85,10 +86,15 @@ class LayeredTransformer(nn.Module):
 
     def _check_room(self, cache: BufferCache, seqlens: List[int]) -> None:
         past = cache._kv_seqlens_host or [0] * len(seqlens)
-        assert max(p + s for p, s in zip(past, seqlens)) <= cache.max_seq_len, "sequence longer than the cache"
+        longest = max(p + s for p, s in zip(past, seqlens))
+        assert longest <= cache.max_seq_len, "sequence longer than the cache"
+        assert self.pos is None or longest <= self.pos.shape[0], f"sequence of {longest} tokens, {self.pos.shape[0]} learned positions"
 
     def _run_layers(self, input_ids: torch.Tensor, md: List[CacheInputMetadata], cache: BufferCache) -> torch.Tensor:
-        x = _h.embed_scale(input_ids, self.embed, self.args.embedding_scale)
+        if self.pos is not None:
+            x = _h.embed_pos(input_ids, md[0].positions, self.embed, self.pos, self.args.embedding_scale)
+        else:
+            x = _h.embed_scale(input_ids, self.embed, self.args.embedding_scale)
         ctx: Dict[str, torch.Tensor] = {}
         lp = self.args.loop
         first_pass = True
@@ -106,7 +112,7 @@ class LayeredTransformer(nn.Module):
 
     def logits_of(self, x32: torch.Tensor) -> torch.Tensor:
         """Final norm + head, fp32 [rows, vocab]."""
-        return _h.linear(self.final_norm(x32), self.head, epi=_h.EPI_F32)
+        return _h.linear(self.final_norm(x32), self.head, epi=_h.EPI_F32, limit=self.args.logit_softcap)
 
     def _graph_decode_ok(self, seqlens: List[int], cache: Optional[BufferCache]) -> bool:
         if cache is None or self._tap is not None or os.environ.get("MB200_DECODE_GRAPH", "1") == "0":
@@ -193,7 +199,9 @@ class LayeredTransformer(nn.Module):
         if k == "embed":
             return put(self.embed)
         if k == "final.norm":
-            return put(self.final_norm.weight)
+            return self.final_norm.load_weight(v)
+        if k == "pos" and self.pos is not None:
+            return put(self.pos)
         if k == "final.norm.b" and self.final_norm.bias is not None:
             return put(self.final_norm.bias)
         if k == "head":
@@ -205,7 +213,7 @@ class LayeredTransformer(nn.Module):
         if base in ("norm1", "norm2", "norm1b", "norm2b") and getattr(blk, base) is not None:
             nrm: Norm = getattr(blk, base)
             if base == rest:
-                return put(nrm.weight)
+                return nrm.load_weight(v)
             if nrm.bias is not None:
                 return put(nrm.bias)
         part, name = rest.split(".", 1) if "." in rest else (rest, "")
@@ -241,7 +249,7 @@ class LayeredTransformer(nn.Module):
         def norm_keys(name: str, nrm: Optional[Norm]) -> List[str]:
             return [] if nrm is None else [name] + ([name + ".b"] if nrm.bias is not None else [])
 
-        keys = ["embed", "head"] + norm_keys("final.norm", self.final_norm)
+        keys = ["embed", "head"] + norm_keys("final.norm", self.final_norm) + (["pos"] if self.pos is not None else [])
         for i, blk in enumerate(self.layers):
             p = f"l{i}."
             for n in ("norm1", "norm1b", "norm2", "norm2b"):

@@ -191,7 +191,8 @@ import math  # noqa: E402
 from typing import Dict  # noqa: E402
 
 from . import _abi_hybrid as _h  # noqa: E402
-from .args import BiasedAttentionArgs, ClampedGluArgs, LatentAttentionArgs, LightningArgs, MoeFfArgs  # noqa: E402
+from .args import (BiasedAttentionArgs, ClampedGluArgs, Hgrn2Args, LatentAttentionArgs, LightningArgs, MlstmArgs, MoeFfArgs,  # noqa: E402
+                   RotaryAttentionArgs, ScaledInputMoeArgs, SideBySideArgs)
 from .rope import scaled_frequencies  # noqa: E402
 from .cache import LayerCacheSpec  # noqa: E402
 
@@ -201,12 +202,13 @@ MOE_SPARSE_MAX_TOKENS = 16  # up to this many tokens a mixture of experts stream
 
 
 class Norm(nn.Module):
-    """The norm of a layered decoder: "rms" (weight) or "layer" (mean removed; weight and bias).  Reads the fp32 residual stream (or
-    an fp32 sublayer output) and either returns the normed rows in the model dtype or adds them, in fp32, to `add_to`."""
+    """The norm of a layered decoder: "rms" (weight), "rms_scalar" (ONE number as weight; kept as a vector of equal entries, so the
+    same kernel serves it) or "layer" (mean removed; weight and bias).  Reads the fp32 residual stream (or an fp32 sublayer output)
+    and either returns the normed rows in the model dtype or adds them, in fp32, to `add_to`."""
 
     def __init__(self, width: int, eps: float, kind: str):
         super().__init__()
-        assert kind in ("rms", "layer"), kind
+        assert kind in ("rms", "rms_scalar", "layer"), kind
         self.kind, self.eps = kind, eps
         self.weight = nn.Parameter(torch.empty(width), requires_grad=False)
         self.bias = nn.Parameter(torch.empty(width), requires_grad=False) if kind == "layer" else None
@@ -217,13 +219,25 @@ class Norm(nn.Module):
         assert add_to is None, "an rms norm after the sublayer is not built"
         return _h.rmsnorm(x32, self.weight, self.eps)
 
+    def load_weight(self, v: torch.Tensor) -> None:
+        """Takes the checkpoint's weight: a vector, or the single number of an "rms_scalar" norm."""
+        if self.kind == "rms_scalar":
+            assert v.numel() == 1, f"a norm with one number got {tuple(v.shape)}"
+            self.weight.copy_(v.reshape(1).expand_as(self.weight))
+        else:
+            assert v.shape == self.weight.shape, f"norm weight {tuple(v.shape)} != {tuple(self.weight.shape)}"
+            self.weight.copy_(v)
 
-def project_out(y: torch.Tensor, w: torch.Tensor, x32: torch.Tensor, post: Optional[Norm]) -> None:
-    """The last Linear of a sublayer: added to the fp32 residual stream by its epilogue, or, when the block norms the sublayer's
-    output first (`post`), written in fp32 and added by the norm kernel."""
-    if post is None:
+
+def project_out(y: torch.Tensor, w: torch.Tensor, x32: torch.Tensor, post: Optional[Norm], scale: float = 1.0) -> None:
+    """The last Linear of a sublayer: added to the fp32 residual stream by its epilogue (times `scale`, for a sublayer that enters a
+    weighted sum), or, when the block norms the sublayer's output first (`post`), written in fp32 and added by the norm kernel."""
+    if post is None and scale != 1.0:
+        _h.linear(y, w, epi=_h.EPI_RESIDUAL_SCALED, residual=x32, alpha=scale)
+    elif post is None:
         _h.linear(y, w, epi=_h.EPI_RESIDUAL, residual=x32)
     else:
+        assert scale == 1.0, "a scaled sublayer with a norm after it is not built"
         post(_h.linear(y, w, epi=_h.EPI_F32), add_to=x32)
 
 
@@ -483,25 +497,290 @@ class MoeFeedForward(nn.Module):
         return True
 
 
-MIXERS = {"attention": BiasedAttention, "lightning": LightningMixer, "latent_attention": LatentAttention}
-FEED_FORWARDS = {ClampedGluArgs: ClampedGLU, MoeFfArgs: MoeFeedForward}
+
+
+class RotaryWindowAttention(nn.Module):
+    """Causal softmax attention with rotary positions, a unit RMS norm of the rotated q and k heads, grouped key/value heads and an
+    optional sliding window (args.RotaryAttentionArgs).  The ring holds min(window, longest sequence) rows per sequence.  A decode
+    step writes its key and value into the ring, then attends over it; a prompt (portion) attends over the OLD ring plus its own
+    keys and values, and writes the ring afterwards, so a prompt longer than the ring still finds every key inside each token's
+    window.  Packed weights: wqkv = q ++ k ++ v rows."""
+
+    def __init__(self, width: int, a: RotaryAttentionArgs, eps: float):
+        super().__init__()
+        self.a, self.eps = a, eps
+        self.nq, self.nk, self.nv = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim
+        self.wqkv = nn.Parameter(torch.empty(self.nq + self.nk + self.nv, width), requires_grad=False)
+        self.wo = nn.Parameter(torch.empty(width, a.heads * a.vdim), requires_grad=False)
+        self._freq: Optional[torch.Tensor] = None
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="ring", n_kv_heads=self.a.kv_heads, k_dim=self.a.dim, v_dim=self.a.vdim, window=self.a.window)
+
+    def frequencies(self) -> torch.Tensor:
+        """float64 [rot_dims / 2]: rot_base^(-2i / rot_dims) / rot_factor, evaluated on the host in double precision."""
+        if self._freq is None or self._freq.device != self.wo.device:
+            f, _ = scaled_frequencies(self.a.rot_dims, self.a.rot_base, None) if self.a.rot_dims else (torch.zeros(0, dtype=torch.float64), 1.0)
+            self._freq = (f / self.a.rot_factor).to(self.wo.device)
+        return self._freq
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor], post: Optional[Norm] = None,
+            scale: float = 1.0) -> None:
+        a, md = self.a, view.metadata
+        T, B, W = hn.shape[0], len(md.seqlens), md.window
+        qkv = _h.linear(hn, self.wqkv)
+        out = torch.empty(T, a.heads * a.vdim, dtype=hn.dtype, device=hn.device)
+        window = a.window or 0
+        if md.prefill:
+            q, k, v = _h.rot_prep(qkv, self.frequencies(), md.positions, None, None, None, a.heads, a.kv_heads, a.dim, a.vdim, a.rot_dims, a.unit_norm,
+                                  self.eps, own=True)
+            _h.attn_window(q, view.cache_k, view.cache_v, md.positions, md.q_start, md.slots, out, B, W, a.heads, a.kv_heads, a.dim, a.vdim, a.scale,
+                           window, own_k=k, own_v=v, seqpos=md.seqpos,
+                           n_tiles=sum((n + 63) // 64 for n in md.seqlens) if md.max_seqlen >= FLASH_MIN_QUERIES else 0)
+            _h.kv_scatter(k, v, md.cache_rows, view.cache_k, view.cache_v)
+        else:
+            q, _, _ = _h.rot_prep(qkv, self.frequencies(), md.positions, md.cache_rows, view.cache_k, view.cache_v, a.heads, a.kv_heads, a.dim, a.vdim,
+                                  a.rot_dims, a.unit_norm, self.eps, own=False)
+            _h.attn_window(q, view.cache_k, view.cache_v, md.positions, md.q_start, md.slots, out, B, W, a.heads, a.kv_heads, a.dim, a.vdim, a.scale,
+                           window, splits=_h.attn_splits(T, a.heads, W))
+        project_out(out, self.wo, x32, post, scale)
+
+    def checkpoint_names(self) -> List[str]:
+        return ["q", "k", "v", "o"]
+
+    def assign(self, name: str, put) -> bool:
+        spans = {"q": (0, self.nq), "k": (self.nq, self.nq + self.nk), "v": (self.nq + self.nk, self.nq + self.nk + self.nv)}
+        if name in spans:
+            put(self.wqkv[spans[name][0]: spans[name][1]])
+        elif name == "o":
+            put(self.wo)
+        else:
+            return False
+        return True
+
+
+class Hgrn2Mixer(nn.Module):
+    """Gated linear recurrence (args.Hgrn2Args): q = silu(W_q h), f = lower + (1 - lower) sigmoid(W_f h + b_f), v = W_v h; per head
+    S <- diag(f) S + (1 - f) v^T, o = S^T q in fp32 (state in the cache); every head RMS-normed with one weight [vdim] shared by the
+    heads.  Packed weights: wqfv = q ++ f ++ v rows, bqfv zero outside the f rows; SiLU on q in the Linear's epilogue."""
+
+    def __init__(self, width: int, a: Hgrn2Args, eps: float):
+        super().__init__()
+        self.a, self.eps = a, eps
+        self.nqk, self.nv = a.heads * a.dim, a.heads * a.vdim
+        self.wqfv = nn.Parameter(torch.empty(2 * self.nqk + self.nv, width), requires_grad=False)
+        self.bqfv = nn.Parameter(torch.empty(2 * self.nqk + self.nv), requires_grad=False)
+        self.lower = nn.Parameter(torch.empty(self.nqk), requires_grad=False)
+        self.norm = nn.Parameter(torch.empty(a.vdim), requires_grad=False)
+        self.wo = nn.Parameter(torch.empty(width, self.nv), requires_grad=False)
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="state", state_shape=(self.a.heads, self.a.dim, self.a.vdim))
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor], post: Optional[Norm] = None,
+            scale: float = 1.0) -> None:
+        a, md = self.a, view.metadata
+        qfv = _h.linear(hn, self.wqfv, self.bqfv, n_act=self.nqk)
+        qab = _h.hgrn2_gates(qfv, self.lower, self.nqk)
+        o32 = _h.gated_scan(qab, qfv, qfv.shape[1], 2 * self.nqk, view.state, md.q_start, md.seqpos, md.slots, len(md.seqlens), a.heads, a.dim, a.vdim,
+                            ones=False)
+        y = _h.scan_post(o32, None, self.norm, False, None, 0, 0, a.heads, a.vdim, False, self.eps)
+        project_out(y, self.wo, x32, post, scale)
+
+    def checkpoint_names(self) -> List[str]:
+        return ["q", "f", "f.b", "lower", "v", "norm", "o"]
+
+    def assign(self, name: str, put) -> bool:
+        n = self.nqk
+        if name == "q":
+            put(self.wqfv[:n])
+        elif name == "f":
+            put(self.wqfv[n: 2 * n])
+        elif name == "v":
+            put(self.wqfv[2 * n:])
+        elif name == "f.b":
+            self.bqfv.zero_()  # q and v have no bias
+            put(self.bqfv[n: 2 * n])
+        elif name in ("lower", "norm"):
+            put(getattr(self, name))
+        elif name == "o":
+            put(self.wo)
+        else:
+            return False
+        return True
+
+
+class SideBySideMixer(nn.Module):
+    """Two mixers on the same input, summed with fixed weights (args.SideBySideArgs): left_scale * rotary window attention +
+    right_scale * gated linear recurrence.  The layer's cache entry holds the attention's ring AND the recurrence's state; each
+    mixer's output Linear adds its weighted result to the residual stream in its epilogue.  Checkpoint names: left.*, right.*."""
+
+    def __init__(self, width: int, a: SideBySideArgs, eps: float):
+        super().__init__()
+        self.a = a
+        self.left = RotaryWindowAttention(width, a.left, eps)
+        self.right = Hgrn2Mixer(width, a.right, eps)
+
+    def cache_spec(self) -> LayerCacheSpec:
+        sp = self.left.cache_spec()
+        sp.state_shape = self.right.cache_spec().state_shape
+        return sp
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor], post: Optional[Norm] = None) -> None:
+        assert post is None, "a norm after a weighted sum of mixers is not built"
+        self.left.run(hn, x32, view, ctx, None, self.a.left_scale)
+        self.right.run(hn, x32, view, ctx, None, self.a.right_scale)
+
+    def checkpoint_names(self) -> List[str]:
+        return ["left." + n for n in self.left.checkpoint_names()] + ["right." + n for n in self.right.checkpoint_names()]
+
+    def assign(self, name: str, put) -> bool:
+        side, _, rest = name.partition(".")
+        if side == "left":
+            return self.left.assign(rest, put)
+        if side == "right":
+            return self.right.assign(rest, put)
+        return False
+
+
+class MlstmMixer(nn.Module):
+    """Matrix memory with exponential gates (args.MlstmArgs).  q = W_q h / sqrt(dim), k, v; per head log gates i = cap tanh(. / cap),
+    f = logsigmoid(cap tanh(. / cap)); m_t = max(f + m_(t-1), i) (m_0 = 0); S <- exp(f + m_(t-1) - m_t) S + exp(i - m_t) k v^T, n
+    likewise with k alone; o = S^T q / (max(|n . q|, exp(-m_t)) + 1e-6); every head divided by its root mean square, times a weight over
+    all heads and sigmoid(W_g h).  The state row of a sequence is [heads, dim, vdim + 1] (the normaliser is the last column: a value
+    that is 1 for every token) followed by the heads' m, all fp32.  Packed weights: wqkvg = q ++ k ++ v ++ g rows; wif = i ++ f rows
+    (+ bif), whose outputs stay fp32."""
+
+    def __init__(self, width: int, a: MlstmArgs, eps: float):
+        super().__init__()
+        self.a, self.eps = a, eps
+        self.nqk, self.nv = a.heads * a.dim, a.heads * a.vdim
+        self.wqkvg = nn.Parameter(torch.empty(2 * self.nqk + 2 * self.nv, width), requires_grad=False)
+        self.wif = nn.Parameter(torch.empty(2 * a.heads, width), requires_grad=False)
+        self.bif = nn.Parameter(torch.empty(2 * a.heads), requires_grad=False)
+        self.norm = nn.Parameter(torch.empty(self.nv), requires_grad=False)
+        self.wo = nn.Parameter(torch.empty(width, self.nv), requires_grad=False)
+        self.m_off = a.heads * a.dim * (a.vdim + 1)
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="state", state_shape=(self.m_off + self.a.heads,))
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor], post: Optional[Norm] = None,
+            scale: float = 1.0) -> None:
+        a, md = self.a, view.metadata
+        B = len(md.seqlens)
+        qkvg = _h.linear(hn, self.wqkvg)
+        gif = _h.linear(hn, self.wif, self.bif, epi=_h.EPI_F32)
+        gates, qab = _h.mlstm_gates(qkvg, gif, view.state, self.m_off, md.q_start, md.seqpos, md.slots, B, a.heads, a.dim, a.gate_cap, a.dim ** -0.5)
+        o32 = _h.gated_scan(qab, qkvg, qkvg.shape[1], 2 * self.nqk, view.state, md.q_start, md.seqpos, md.slots, B, a.heads, a.dim, a.vdim, ones=True)
+        y = _h.scan_post(o32, gates, self.norm, True, qkvg, qkvg.shape[1], 2 * self.nqk + self.nv, a.heads, a.vdim, True, self.eps)
+        project_out(y, self.wo, x32, post, scale)
+
+    def checkpoint_names(self) -> List[str]:
+        return ["q", "k", "v", "g", "i", "i.b", "f", "f.b", "norm", "o"]
+
+    def assign(self, name: str, put) -> bool:
+        H = self.a.heads
+        o = [0, self.nqk, 2 * self.nqk, 2 * self.nqk + self.nv, 2 * self.nqk + 2 * self.nv]
+        idx = {"q": 0, "k": 1, "v": 2, "g": 3}
+        if name in idx:
+            put(self.wqkvg[o[idx[name]]: o[idx[name] + 1]])
+        elif name in ("i", "f"):
+            put(self.wif[:H] if name == "i" else self.wif[H:])
+        elif name in ("i.b", "f.b"):
+            put(self.bif[:H] if name == "i.b" else self.bif[H:])
+        elif name == "norm":
+            put(self.norm)
+        elif name == "o":
+            put(self.wo)
+        else:
+            return False
+        return True
+
+
+class ScaledInputMoe(nn.Module):
+    """Mixture of clamped gated experts whose INPUT is scaled by the routing weight (args.ScaledInputMoeArgs): fp32 sigmoid router,
+    the `top` largest scores chosen, output = sum over the chosen of expert(score * h) + shared(h).  Packed like MoeFeedForward (w13
+    [E * 2 * ff, width] interleaved gate/up rows, w2 [width, E * ff]).  W (s h) = s (W h), so the score multiplies gate and up of the
+    expert's hidden units before the clamps: few tokens stream only the chosen experts, prompts run all experts as two Linears with the
+    score (0 when not chosen, which gives exactly 0) applied in the first one's epilogue."""
+
+    def __init__(self, width: int, a: ScaledInputMoeArgs):
+        super().__init__()
+        self.a, self.width = a, width
+        self.router = nn.Parameter(torch.empty(a.experts, width), requires_grad=False)
+        self.w13 = nn.Parameter(torch.empty(a.experts * 2 * a.ff, width), requires_grad=False)
+        self.w2 = nn.Parameter(torch.empty(width, a.experts * a.ff), requires_grad=False)
+        self.shared = ClampedGLU(width, a.shared) if a.shared is not None else None
+        self.sparse_max_tokens = MOE_SPARSE_MAX_TOKENS
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, post: Optional[Norm] = None) -> None:
+        assert post is None, "a norm after this feed-forward is not built"
+        a = self.a
+        dense, idx, wsel = _h.moe_route(hn, self.router, None, 1, 1, a.top, score=1)
+        if hn.shape[0] <= self.sparse_max_tokens:
+            x32.add_(_h.moe_sparse(hn, self.w13, self.w2, idx, wsel, a.experts, a.ff, glu=True, limit=a.limit, alpha=a.alpha))
+        else:
+            act = _h.linear_glu(hn, self.w13, a.limit, a.alpha, rowscale=dense, group=a.ff)
+            _h.linear(act, self.w2, epi=_h.EPI_RESIDUAL, residual=x32)
+        if self.shared is not None:
+            self.shared.run(hn, x32)
+
+    def checkpoint_names(self) -> List[str]:
+        names = ["router"] + [f"e{e}.{n}" for e in range(self.a.experts) for n in ("gate", "up", "down")]
+        return names + (["shared." + n for n in self.shared.checkpoint_names()] if self.shared is not None else [])
+
+    def assign(self, name: str, put) -> bool:
+        a = self.a
+        head, _, part = name.partition(".")
+        if name == "router":
+            put(self.router)
+        elif head == "shared" and self.shared is not None:
+            return self.shared.assign(part, put)
+        elif head[:1] == "e" and head[1:].isdigit() and int(head[1:]) < a.experts:
+            e = int(head[1:])
+            if part == "gate":
+                put(self.w13.view(a.experts, a.ff, 2, self.width)[e, :, 0])
+            elif part == "up":
+                put(self.w13.view(a.experts, a.ff, 2, self.width)[e, :, 1])
+            elif part == "down":
+                put(self.w2.view(self.width, a.experts, a.ff)[:, e])
+            else:
+                return False
+        else:
+            return False
+        return True
+
+
+MIXERS = {"attention": BiasedAttention, "lightning": LightningMixer, "latent_attention": LatentAttention, "parallel": SideBySideMixer,
+          "mlstm": MlstmMixer, "mlstm_2": MlstmMixer}
+FEED_FORWARDS = {ClampedGluArgs: ClampedGLU, MoeFfArgs: MoeFeedForward, ScaledInputMoeArgs: ScaledInputMoe}
 
 
 class LayeredBlock(nn.Module):
     """x <- x + mixer(norm1(x)); x <- x + ff(norm2(x)) when the layer has a feed-forward; with `post_norm` each sublayer's output
-    goes through a norm of its own (norm1b, norm2b) before it is added.  `x32` is updated in place."""
+    goes through a norm of its own (norm1b, norm2b) before it is added.  `parallel`: one norm, h = norm1(x), and both sublayers read
+    it: x <- x + mixer(h) + ff(h).  `x32` is updated in place."""
 
-    def __init__(self, width: int, eps: float, mixer: nn.Module, mlp: Optional[nn.Module], norm: str = "rms", post_norm: bool = False):
+    def __init__(self, width: int, eps: float, mixer: nn.Module, mlp: Optional[nn.Module], norm: str = "rms", post_norm: bool = False,
+                 parallel: bool = False):
         super().__init__()
-        self.eps = eps
+        assert not (parallel and post_norm), "a parallel block with norms after the sublayers is not built"
+        self.eps, self.parallel = eps, parallel
         self.norm1 = Norm(width, eps, norm)
         self.norm1b = Norm(width, eps, norm) if post_norm else None
         self.mix = mixer
         self.mlp = mlp
-        self.norm2 = Norm(width, eps, norm) if mlp is not None else None
+        self.norm2 = Norm(width, eps, norm) if mlp is not None and not parallel else None
         self.norm2b = Norm(width, eps, norm) if mlp is not None and post_norm else None
 
     def forward(self, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor]) -> torch.Tensor:
+        if self.parallel:  # the sublayers read hn only, so each may add its output to the stream as it finishes
+            hn = self.norm1(x32)
+            self.mix.run(hn, x32, view, ctx, None)
+            if self.mlp is not None:
+                self.mlp.run(hn, x32, None)
+            return x32
         self.mix.run(self.norm1(x32), x32, view, ctx, self.norm1b)
         if self.mlp is not None:
             self.mlp.run(self.norm2(x32), x32, self.norm2b)
