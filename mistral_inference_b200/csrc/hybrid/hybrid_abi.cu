@@ -178,7 +178,6 @@ int mbh_attn_window(const void* q, const void* cache_k, const void* cache_v, con
     if (H % G) return bad("mbh_attn_bias: heads must be a multiple of kv heads");
     if (splits > AT_MAX_SPLITS) return bad("mbh_attn_bias: at most 64 splits");
     if (window < 0 || (!own_k != !own_v) || (own_k && !seqpos)) return bad("mbh_attn_window: window >= 0; own keys, own values and seqpos come together");
-    if (!own_k && window > W) return bad("mbh_attn_window: a ring shorter than the window needs the call's own keys");
     AttnArgs a{q, cache_k, cache_v, (const float*)bias_tab, (int)n_tab, (const int*)positions, (const int*)q_start, (const int*)slots, out,
                (int)T, (int)B, (int)W, (int)H, (int)G, (int)d, (int)e, scale, (int)(splits > 1 && scratch ? splits : 1), (float*)scratch, 0, 0,
                (int)window, own_k, own_v, (const int*)seqpos};

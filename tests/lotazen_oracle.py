@@ -9,7 +9,7 @@ from typing import Dict, List, Optional
 import torch
 
 
-def gelu_sigmoid_glu(h, gate, up, down, limit: float):
+def clamped_glu(h, gate, up, down, limit: float):
     """Clamped gated unit: g = min(W_g h, limit), u = clamp(W_u h, +-limit), y = g sigmoid(1.702 g) (u + 1), out = W_d y."""
     g = (gate @ h).clamp(max=limit)
     u = (up @ h).clamp(min=-limit, max=limit)
@@ -54,15 +54,15 @@ def window_attention(hs, w: Dict[str, torch.Tensor], p: str, a: dict, eps: float
             q = rotate_pairs(q, t, float(rot["base"]), int(rot["dims"]), f)
             k = rotate_pairs(k, t, float(rot["base"]), int(rot["dims"]), f)
         qs.append(unit_rms(q, eps)); ks.append(unit_rms(k, eps)); vs.append(v)
+    K, V = torch.stack(ks), torch.stack(vs)  # [T, G, d], [T, G, e]
     out = []
     for t in range(T):
-        lo = 0 if win is None else max(0, t - win + 1)
+        lo = 0 if win is None else max(0, t - win + 1)  # the token sees itself and the win - 1 tokens before it
         heads = []
         for h in range(H):
             g = h // (H // G)
-            sc = torch.stack([(qs[t][h] * ks[j][g]).sum() * a["scale"] for j in range(lo, t + 1)])
-            pr = torch.softmax(sc, 0)
-            heads.append(sum(pr[j - lo] * vs[j][g] for j in range(lo, t + 1)))
+            pr = torch.softmax(K[lo:t + 1, g] @ qs[t][h] * a["scale"], 0)
+            heads.append(pr @ V[lo:t + 1, g])
         out.append(w[p + "o"] @ torch.cat(heads))
     return torch.stack(out)
 
@@ -125,9 +125,9 @@ def moe(hs, w: Dict[str, torch.Tensor], p: str, a: dict):
         idx, wt = route(hs[t], w[p + "router"], int(a["router"]["top"]))
         y = torch.zeros_like(hs[t])
         for e, s in zip(idx, wt):
-            y = y + gelu_sigmoid_glu(s * hs[t], w[f"{p}e{e}.gate"], w[f"{p}e{e}.up"], w[f"{p}e{e}.down"], float(a["expert"]["limit"]))
+            y = y + clamped_glu(s * hs[t], w[f"{p}e{e}.gate"], w[f"{p}e{e}.up"], w[f"{p}e{e}.down"], float(a["expert"]["limit"]))
         if a.get("shared"):
-            y = y + gelu_sigmoid_glu(hs[t], w[p + "shared.gate"], w[p + "shared.up"], w[p + "shared.down"], float(a["shared"]["limit"]))
+            y = y + clamped_glu(hs[t], w[p + "shared.gate"], w[p + "shared.up"], w[p + "shared.down"], float(a["shared"]["limit"]))
         out.append(y)
     return torch.stack(out)
 
@@ -154,5 +154,5 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], taps: Opti
         if taps is not None:
             taps.append(x.clone())
     z = scalar_rms_norm(x, w["final.norm"], eps) @ w["head"].t()
-    cap = float(cfg["logit_softcap"])
-    return cap * torch.tanh(z / cap)
+    cap = float(cfg.get("logit_softcap") or 0.0)
+    return cap * torch.tanh(z / cap) if cap > 0 else z
