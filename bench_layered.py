@@ -1,8 +1,9 @@
-"""`bench.py --design fesenex|taruvik`: prefill and decode throughput of the layered decoder at layer sizes of real models (random
+"""`bench.py --design fesenex|taruvik|lotazen`: prefill and decode throughput of the layered decoder at layer sizes of real models (random
 weights), beside the dense `Transformer` of equal width / heads / feed-forward size / depth / vocabulary, plus the time of each
 hybrid kernel at those shapes against its roofline (bf16 tensor peak or HBM copy bandwidth from MEASURED_PEAKS.json).
 For `taruvik` (latent attention, mixture of experts) the neighbour is the `Transformer` with a mixture of experts of equal
-width / heads / experts / depth.  Timed with CUDA events after warm-up; the prompt batch and the weights exceed L2 at the larger size, and L2 is flushed between
+width / heads / experts / depth; for `lotazen` (rotary window attention beside a gated recurrence, matrix memories, experts with scaled
+input) it is the Fesenex design at equal width / heads / depth, and every new kernel is timed next to the like kernel at the same shape.  Timed with CUDA events after warm-up; the prompt batch and the weights exceed L2 at the larger size, and L2 is flushed between
 timed kernel launches.  Prints one JSON line."""
 import json
 import math
@@ -24,7 +25,7 @@ def layered_config(s: dict) -> dict:
                                           "decay": [math.exp(-1.0 / (4 + 8 * h)) for h in range(s["lin_heads"])]},
            "mlp": {"kind": "dense", "ff": s["ff"], "limit": 7.0}}
     return {"architecture": "Fesenex", "vocab": s["vocab"], "width": s["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
-            "layers": [lin if i % 4 == 3 else att for i in range(s["layers"])]}
+            "layers": [lin if (i in s["lightning_at"] if "lightning_at" in s else i % 4 == 3) else att for i in range(s["layers"])]}
 
 
 def build_layered(s: dict, dev):
@@ -337,9 +338,204 @@ def run_taruvik(a, peaks: dict) -> dict:
     return res
 
 
+# ----------------------------------------------------------------------------------------------- Lotazen
+LOTAZEN_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, rec_heads=16, experts=16, top=2, ff=1408, shared_ff=2816, vocab=32768,
+                  order="ppmp", lin_heads=16),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, window=2048, rec_heads=32, experts=8, top=2, ff=3584, shared_ff=7168, vocab=32768,
+                  order="pm", lin_heads=32),
+}
+
+
+def lotazen_config(s: dict) -> dict:
+    d = s["dim"]
+    side = {"type": "parallel", "mixer": {
+        "left": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": s["window"]},
+                 "rot": {"base": 500000.0, "dims": d, "scaling": {"factor": 2.0}}},
+        "right": {"heads": s["rec_heads"], "dim": d, "vdim": d}, "left_scale": 0.6, "right_scale": 0.5}}
+    mem = {"type": "mlstm", "mixer": {"heads": s["rec_heads"], "dim": d, "vdim": d, "gate_cap": 12.0}}
+    mlp = {"kind": "moe", "expert": {"ff": s["ff"], "limit": 7.0}, "router": {"experts": s["experts"], "top": s["top"]},
+           "shared": {"ff": s["shared_ff"], "limit": 7.0}}
+    return {"architecture": "Lotazen", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5}, "max_positions": 8192, "logit_softcap": 30.0,
+            "layers": [{**(side if c == "p" else mem), "mlp": mlp} for c in s["order"]]}
+
+
+def build_lotazen(s: dict, dev):
+    from mistral_inference_b200.args import LayeredArgs
+    from mistral_inference_b200.layered import LayeredTransformer
+
+    m = LayeredTransformer.empty(LayeredArgs.from_dict(lotazen_config(s)), dev, torch.bfloat16)
+    g = torch.Generator(device=dev).manual_seed(0)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            last = n.rsplit(".", 1)[-1]
+            if p.dim() >= 2:
+                p.copy_(torch.randn(p.shape, generator=g, device=dev, dtype=torch.float32) / math.sqrt(p.shape[-1]))
+            elif last in ("weight", "norm"):
+                p.fill_(1.0)
+            elif last == "lower":
+                p.copy_(torch.rand(p.shape, generator=g, device=dev) * 0.9)
+            else:
+                p.copy_(torch.randn(p.shape, generator=g, device=dev, dtype=torch.float32) * 0.1)
+    return m.eval()
+
+
+def fesenex_like(s: dict) -> dict:
+    """The closest existing design at equal size: attention layers of the same heads where Lotazen has attention beside a recurrence,
+    a lightning layer where it has a matrix memory, a dense feed-forward of the size of the experts one token uses."""
+    return dict(width=s["width"], heads=s["heads"], kv_heads=s["kv_heads"], dim=s["dim"], ff=s["top"] * s["ff"] + s["shared_ff"], vocab=s["vocab"],
+                layers=len(s["order"]), lin_heads=s["lin_heads"], lightning_at=[i for i, c in enumerate(s["order"]) if c == "m"])
+
+
+def lotazen_kernel_table(s: dict, T: int, ctx: int, peaks: dict, dev) -> dict:
+    """Every kernel the design added, alone at this size, each next to the like kernel of the closest design at the same shape."""
+    from mistral_inference_b200 import _abi_hybrid as h
+    from mistral_inference_b200.cache import BufferCache, LayerCacheSpec
+
+    bf = torch.bfloat16
+    W, H, G, d, win, RH, E, ff, top = (s[k] for k in ("width", "heads", "kv_heads", "dim", "window", "rec_heads", "experts", "ff", "top"))
+    flush = torch.zeros(160 << 20, dtype=torch.float32, device=dev)
+    rows = {}
+
+    def rec(name, ms, flops=0.0, bytes_=0.0, note=None):
+        r = {"ms": round(ms, 4)}
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 2)
+            r["of_bf16_peak"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)
+        if bytes_:
+            r["gb_s"] = round(bytes_ / ms / 1e6, 1)
+            r["of_hbm_peak"] = round(bytes_ / ms / 1e6 / peaks["hbm_gbs"], 3)
+        if note:
+            r["note"] = note
+        rows[name] = r
+
+    B = 8
+    # ---- attention: a prompt through the window, then one token per sequence
+    ring = BufferCache(1, B, ctx + 8, 0, 0, None, layer_specs=[LayerCacheSpec(kind="ring", n_kv_heads=G, k_dim=d, v_dim=d, window=win)]).to(dev, bf)
+    full = BufferCache(1, B, ctx + 8, 0, 0, None, layer_specs=[LayerCacheSpec(kind="ring", n_kv_heads=G, k_dim=d, v_dim=d)]).to(dev, bf)
+    for c in (ring, full):
+        c.cache_k[0].normal_(); c.cache_v[0].normal_()
+    md = ring.get_input_metadata([T])[0]
+    mdf = full.get_input_metadata([T])[0]
+    qkv = torch.randn(T, (H + 2 * G) * d, device=dev).to(bf)
+    freq = (torch.tensor(500000.0, dtype=torch.float64) ** (-torch.arange(0, d, 2, dtype=torch.float64) / d) / 2.0).to(dev)
+    rec("rot_prep prompt", _time(lambda: h.rot_prep(qkv, freq, md.positions, None, None, None, H, G, d, d, d, True, 1e-5, own=True), 3, 8, flush),
+        bytes_=2.0 * qkv.numel() * 2)
+    q, k, v = h.rot_prep(qkv, freq, md.positions, None, None, None, H, G, d, d, d, True, 1e-5, own=True)
+    o = torch.empty(T, H * d, device=dev, dtype=bf)
+    nt = (T + 63) // 64
+    pairs = sum(min(p + 1, win) for p in range(T))  # (query, key) pairs inside the window
+    rec(f"attn_window prompt (tensor-core kernel, window {win})",
+        _time(lambda: h.attn_window(q, ring.cache_k[0], ring.cache_v[0], md.positions, md.q_start, md.slots, o, 1, md.window, H, G, d, d, 0.09, win, own_k=k, own_v=v,
+                                    seqpos=md.seqpos, n_tiles=nt), 2, 5, flush), flops=4.0 * d * H * pairs)
+    tab = torch.zeros(64, H, device=dev)
+    rec("like: attn_bias_flash prompt (all keys)",
+        _time(lambda: h.attn_bias(q, full.cache_k[0], full.cache_v[0], tab, mdf.positions, mdf.q_start, mdf.slots, o, 1, ctx + 8, H, G, d, d, 0.09, n_tiles=nt), 2, 5, flush),
+        flops=4.0 * d * H * T * (T + 1) / 2)
+    rec("kv_scatter prompt", _time(lambda: h.kv_scatter(k, v, md.cache_rows, ring.cache_k[0], ring.cache_v[0]), 3, 8, flush), bytes_=2.0 * min(T, win) * 2 * G * d * 2)
+    for c in (ring, full):
+        c.reset(); c.init_kvseqlens(B); c.update_seqlens([ctx] * B)
+    md2, md2f = ring.get_input_metadata([1] * B)[0], full.get_input_metadata([1] * B)[0]
+    q2, o2 = q[:B].contiguous(), torch.empty(B, H * d, device=dev, dtype=bf)
+    rec(f"attn_window decode B={B} (ring of {md2.window})",
+        _time(lambda: h.attn_window(q2, ring.cache_k[0], ring.cache_v[0], md2.positions, md2.q_start, md2.slots, o2, B, md2.window, H, G, d, d, 0.09, win,
+                                    splits=h.attn_splits(B, H, md2.window)), 3, 8, flush), bytes_=2.0 * B * min(ctx + 1, win) * G * d * 2)
+    rec(f"like: attn_bias decode B={B} ctx={ctx}",
+        _time(lambda: h.attn_bias(q2, full.cache_k[0], full.cache_v[0], tab, md2f.positions, md2f.q_start, md2f.slots, o2, B, ctx + 8, H, G, d, d, 0.09,
+                                  splits=h.attn_splits(B, H, ctx + 8)), 3, 8, flush), bytes_=2.0 * B * (ctx + 1) * G * d * 2)
+    # ---- recurrences
+    Hd = RH * d
+    qfv = (torch.randn(T, 3 * Hd, device=dev) * 0.3).to(bf)
+    lower = (torch.rand(Hd, device=dev) * 0.9).to(bf)
+    rec("hgrn2_gates prompt", _time(lambda: h.hgrn2_gates(qfv, lower, Hd), 3, 8, flush), bytes_=T * Hd * (2 * 2 + 3 * 4.0))
+    qab = h.hgrn2_gates(qfv, lower, Hd)
+    state = torch.zeros(B, RH, d, d, device=dev)
+    zero = torch.zeros(1, dtype=torch.int32, device=dev)
+    rec("gated_scan prompt (HGRN2)", _time(lambda: h.gated_scan(qab, qfv, 3 * Hd, 2 * Hd, state, md.q_start, zero, md.slots, 1, RH, d, d, ones=False), 2, 5, flush),
+        flops=4.0 * T * RH * d * d, note="one CTA column walks the sequence, fp32 FMA")
+    rec("gated_scan prompt (HGRN2), chunk-parallel",
+        _time(lambda: h.gated_scan(qab, qfv, 3 * Hd, 2 * Hd, state, md.q_start, zero, md.slots, 1, RH, d, d, ones=False, max_seqlen=T), 2, 5, flush),
+        flops=4.0 * T * RH * d * d, note="useful FLOPs; the chunks run twice (local state, then outputs), fp32 FMA")
+    qkvg = torch.randn(T, 4 * Hd, device=dev).to(bf) * 0.1
+    lstate = torch.zeros(B, RH, d, d, device=dev)
+    decay = torch.full((RH,), 0.97, device=dev)
+    o32 = torch.empty(T, Hd, device=dev)
+    rec("like: lightning_scan prompt", _time(lambda: h.lightning_scan(qkvg, lstate, decay, md.q_start, zero, md.slots, o32, 1, RH, d, d), 2, 5, flush),
+        flops=4.0 * T * RH * d * d, note="sequential in the tokens, fp32 FMA")
+    mstate = torch.zeros(B, RH * d * (d + 1) + RH, device=dev)
+    gif = torch.randn(T, 2 * RH, device=dev)
+    rec("mlstm_gates prompt", _time(lambda: h.mlstm_gates(qkvg, gif, mstate, RH * d * (d + 1), md.q_start, zero, md.slots, 1, RH, d, 12.0, d ** -0.5), 3, 8, flush),
+        bytes_=T * Hd * (2 * 2 + 3 * 4.0), note="includes the running maximum, one warp per head over all tokens")
+    gates, qab2 = h.mlstm_gates(qkvg, gif, mstate, RH * d * (d + 1), md.q_start, zero, md.slots, 1, RH, d, 12.0, d ** -0.5)
+    rec("gated_scan prompt (mLSTM, normaliser column)",
+        _time(lambda: h.gated_scan(qab2, qkvg, 4 * Hd, 2 * Hd, mstate, md.q_start, zero, md.slots, 1, RH, d, d, ones=True), 2, 5, flush), flops=4.0 * T * RH * d * (d + 1))
+    rec("gated_scan prompt (mLSTM, normaliser column), chunk-parallel",
+        _time(lambda: h.gated_scan(qab2, qkvg, 4 * Hd, 2 * Hd, mstate, md.q_start, zero, md.slots, 1, RH, d, d, ones=True, max_seqlen=T), 2, 5, flush),
+        flops=4.0 * T * RH * d * (d + 1))
+    om = h.gated_scan(qab2, qkvg, 4 * Hd, 2 * Hd, mstate, md.q_start, zero, md.slots, 1, RH, d, d, ones=True)
+    nw = torch.ones(Hd, device=dev).to(bf)
+    rec("scan_post prompt (mLSTM)", _time(lambda: h.scan_post(om, gates, nw, True, qkvg, 4 * Hd, 3 * Hd, RH, d, True, 1e-5), 3, 8, flush), bytes_=T * Hd * (4 + 2 + 2.0))
+    rec("like: gated_headnorm prompt", _time(lambda: h.gated_headnorm(o32, nw, qkvg, 4 * Hd, 3 * Hd, 1e-5), 3, 8, flush), bytes_=T * Hd * (4 + 2 + 2.0))
+    one = torch.ones(B, dtype=torch.int32, device=dev)
+    qabB = qab[:B].contiguous()
+    rec(f"gated_scan decode B={B} (HGRN2)", _time(lambda: h.gated_scan(qabB, qfv, 3 * Hd, 2 * Hd, state, md2.q_start, one, md2.slots, B, RH, d, d, ones=False), 3, 8, flush),
+        bytes_=2.0 * state.numel() * 4)
+    rec(f"like: lightning_scan decode B={B}", _time(lambda: h.lightning_scan(qkvg, lstate, decay, md2.q_start, one, md2.slots, o32, B, RH, d, d), 3, 8, flush),
+        bytes_=2.0 * lstate.numel() * 4)
+    # ---- experts
+    x = torch.randn(T, W, device=dev).to(bf)
+    wr = (torch.randn(E, W, device=dev) / math.sqrt(W) * 4).to(bf)
+    rec("moe_route prompt (sigmoid)", _time(lambda: h.moe_route(x, wr, None, 1, 1, top, score=1), 3, 8, flush), bytes_=T * W * 2.0)
+    dense, idx, wsel = h.moe_route(x, wr, None, 1, 1, top, score=1)
+    w13 = (torch.randn(E * 2 * ff, W, device=dev) * 0.02).to(bf)
+    w2 = (torch.randn(W, E * ff, device=dev) * 0.02).to(bf)
+    x32 = torch.zeros(T, W, device=dev)
+
+    def dense_form():
+        act = h.linear_glu(x, w13, 7.0, 1.702, rowscale=dense, group=ff)
+        return h.linear(act, w2, epi=h.EPI_RESIDUAL, residual=x32)
+
+    def dense_like():
+        act = h.linear_swiglu(x, w13, rowscale=dense, group=ff)
+        return h.linear(act, w2, epi=h.EPI_F32)
+
+    rec("experts prompt (all experts, scaled input, masked)", _time(dense_form, 2, 5, flush), flops=6.0 * T * top * ff * W,
+        note=f"useful FLOPs (top {top} of {E}); the kernels compute all {E} experts")
+    rec("like: experts prompt of the softmax-routed mixture", _time(dense_like, 2, 5, flush), flops=6.0 * T * top * ff * W)
+    for M in (1, B):
+        xs, ii, ww = x[:M].contiguous(), idx[:M].contiguous(), wsel[:M].contiguous()
+        rec(f"experts decode (chosen only, scaled input) M={M}", _time(lambda: h.moe_sparse(xs, w13, w2, ii, ww, E, ff, glu=True, limit=7.0, alpha=1.702), 3, 8, flush),
+            bytes_=M * top * 3.0 * ff * W * 2)
+        rec(f"like: experts decode of the softmax-routed mixture M={M}", _time(lambda: h.moe_sparse(xs, w13, w2, ii, ww, E, ff), 3, 8, flush),
+            bytes_=M * top * 3.0 * ff * W * 2)
+    return rows
+
+
+def run_lotazen(a, peaks: dict) -> dict:
+    dev = torch.device("cuda", torch.cuda.current_device())
+    T, ctx = a.prefill, a.prefill
+    res = {"design": "Lotazen", "dtype": "bf16", "data": "synthetic", "prompt_tokens": T, "peaks": {k: peaks.get(k) for k in ("hbm_gbs", "bf16_tflops")}, "sizes": {}}
+    for name, s in LOTAZEN_SIZES.items():
+        t0 = time.time()
+        m = build_lotazen(s, dev)
+        new = end_to_end(m, s["vocab"], T, ctx, (1, 8), a.warmup, a.steps, dev)
+        del m
+        torch.cuda.empty_cache()
+        f = fesenex_like(s)
+        d = build_layered(f, dev)
+        old = end_to_end(d, s["vocab"], T, ctx, (1, 8), a.warmup, a.steps, dev)
+        del d
+        torch.cuda.empty_cache()
+        res["sizes"][name] = {"config": s, "layered": new, "fesenex_equal_size": old, "kernels": lotazen_kernel_table(s, T, ctx, peaks, dev),
+                              "seconds": round(time.time() - t0, 1)}
+    return res
+
+
 def run(a, peaks: dict) -> dict:
     if a.design == "taruvik":
         return run_taruvik(a, peaks)
+    if a.design == "lotazen":
+        return run_lotazen(a, peaks)
     dev = torch.device("cuda", torch.cuda.current_device())
     T, ctx = a.prefill, a.prefill
     res = {"design": "Fesenex", "dtype": "bf16", "data": "synthetic", "prompt_tokens": T, "peaks": {k: peaks.get(k) for k in ("hbm_gbs", "bf16_tflops")}, "sizes": {}}

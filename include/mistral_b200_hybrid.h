@@ -168,9 +168,13 @@ int mbh_kv_scatter(const void* k, const void* v, const void* cache_rows, void* r
 /* Gated linear recurrence per head: S <- diag(a_t) S + b_t v_t^T, o_t = S^T q_t.  qab fp32 [T, 3, H*d] = q | a | b; value (t, h, c) at
  * v[t * v_pitch + v_off + h*e + c] (storage type); state fp32 [slots, state_stride], head h's matrix [d, e + ones] at h * d * (e + ones),
  * read (unless seqpos[b] == 0: zero) and written back; o32 fp32 [T, H * (e + ones)].  ones = 1: one more state column whose value is 1
- * for every token (a normaliser n <- a n + b; o32 has n . q there). */
+ * for every token (a normaliser n <- a n + b; o32 has n . q there).
+ * chunks > 1 (long prompts): the same recurrence chunk-parallel, `chunks` = ceil(longest sequence / chunk_len) chunks of chunk_len
+ * tokens per sequence; scratch: fp32 [B*H*chunks*d*(e + ones + 1)].  chunks <= 1: one CTA column walks each sequence; no scratch.
+ * Key sizes above 128 are split into blocks of 128 keys over CTAs that add their partial outputs into o32 (T tokens, zeroed first). */
 int mbh_gated_scan(const void* qab, const void* v, int64_t v_pitch, int64_t v_off, void* state, int64_t state_stride, const void* q_start,
-                   const void* seqpos, const void* slots, void* o32, int64_t B, int64_t H, int64_t d, int64_t e, int ones, int dt, void* stream);
+                   const void* seqpos, const void* slots, void* o32, int64_t T, int64_t B, int64_t H, int64_t d, int64_t e, int ones,
+                   int64_t chunk_len, int64_t chunks, void* scratch, int dt, void* stream);
 
 /* HGRN2 gates from qfv [T, pitch] = silu(q) | f_pre | v: f = lower + (1 - lower) * sigmoid(f_pre); qab [T, 3, Hd] = q | f | 1 - f. */
 int mbh_hgrn2_gates(const void* qfv, const void* lower, void* qab, int64_t T, int64_t Hd, int64_t pitch, int dt, void* stream);

@@ -49,7 +49,7 @@ _SIGNATURES = {
     "mbh_embed_pos": (c_int, [P, P, P, P, F, P, I, I, c_int, P]),
     "mbh_rot_prep": (c_int, [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, c_int, F, c_int, P]),
     "mbh_kv_scatter": (c_int, [P, P, P, P, P, I, I, I, c_int, P]),
-    "mbh_gated_scan": (c_int, [P, P, I, I, P, I, P, P, P, P, I, I, I, I, c_int, c_int, P]),
+    "mbh_gated_scan": (c_int, [P, P, I, I, P, I, P, P, P, P, I, I, I, I, I, c_int, I, I, P, c_int, P]),
     "mbh_hgrn2_gates": (c_int, [P, P, P, I, I, I, c_int, P]),
     "mbh_mlstm_gates": (c_int, [P, P, P, P, P, I, I, P, P, P, I, I, I, I, I, F, F, c_int, P]),
     "mbh_scan_post": (c_int, [P, P, P, c_int, P, I, I, P, I, I, I, c_int, F, c_int, P]),
@@ -380,13 +380,24 @@ def attn_window(q, cache_k, cache_v, positions, q_start, slots, out, B: int, W: 
 
 
 # ------------------------------------------------------------------------------------------------ gated linear recurrences
-def gated_scan(qab, v, v_pitch: int, v_off: int, state, q_start, seqpos, slots, B: int, H: int, d: int, e: int, ones: bool) -> torch.Tensor:
-    """fp32 [T, H * (e + ones)] of S <- diag(a) S + b v^T, o = S^T q; the state rows of `slots` are read and written."""
+SCAN_CHUNK = 256       # tokens per chunk of the chunk-parallel scan
+SCAN_CHUNK_FROM = 512  # sequences (portions) at least this long run chunk-parallel
+
+
+def gated_scan(qab, v, v_pitch: int, v_off: int, state, q_start, seqpos, slots, B: int, H: int, d: int, e: int, ones: bool,
+               max_seqlen: int = 0) -> torch.Tensor:
+    """fp32 [T, H * (e + ones)] of S <- diag(a) S + b v^T, o = S^T q; the state rows of `slots` are read and written.  With the
+    longest sequence of the call given and at least SCAN_CHUNK_FROM, the scan runs chunk-parallel (same recurrence, fp32)."""
     assert qab.dtype == torch.float32 and state.dtype == torch.float32
     T = qab.shape[0]
-    o = torch.empty(T, H * (e + int(ones)), dtype=torch.float32, device=qab.device)
-    _check(lib().mbh_gated_scan(_ptr(qab), _ptr(v), v_pitch, v_off, _ptr(state), state[0].numel(), _ptr(q_start), _ptr(seqpos), _ptr(slots), _ptr(o), B, H, d,
-                                e, int(ones), dt_of(v.dtype), _stream()), "mbh_gated_scan")
+    ec = e + int(ones)
+    o = torch.empty(T, H * ec, dtype=torch.float32, device=qab.device)
+    chunks, scratch = 1, None
+    if max_seqlen >= SCAN_CHUNK_FROM and max_seqlen > SCAN_CHUNK:
+        chunks = (max_seqlen + SCAN_CHUNK - 1) // SCAN_CHUNK
+        scratch = torch.empty(B * H * chunks * d * (ec + 1), dtype=torch.float32, device=qab.device)
+    _check(lib().mbh_gated_scan(_ptr(qab), _ptr(v), v_pitch, v_off, _ptr(state), state[0].numel(), _ptr(q_start), _ptr(seqpos), _ptr(slots), _ptr(o), T, B, H, d,
+                                e, int(ones), SCAN_CHUNK, chunks, _ptr(scratch), dt_of(v.dtype), _stream()), "mbh_gated_scan")
     return o
 
 

@@ -44,10 +44,29 @@ static cudaError_t launch_lightning(const LightningArgs& a, cudaStream_t st) {
 
 template <typename T>
 static cudaError_t launch_gated_scan(const GatedScanArgs& a, cudaStream_t st) {
-    dim3 grid(a.B * a.H, (a.e + a.ones + GS_THREADS - 1) / GS_THREADS);
-    if (a.d <= 32) gated_scan_kernel<T, 32, 16><<<grid, GS_THREADS, 0, st>>>(a);
-    else if (a.d <= 64) gated_scan_kernel<T, 64, 16><<<grid, GS_THREADS, 0, st>>>(a);
-    else gated_scan_kernel<T, 128, 8><<<grid, GS_THREADS, 0, st>>>(a);
+    dim3 grid(a.B * a.H, (a.e + a.ones + GS_THREADS - 1) / GS_THREADS * a.key_blocks);
+    if (a.d <= 32) gated_scan_kernel<T, 32, 16, GS_WHOLE><<<grid, GS_THREADS, 0, st>>>(a);
+    else if (a.d <= 64) gated_scan_kernel<T, 64, 16, GS_WHOLE><<<grid, GS_THREADS, 0, st>>>(a);
+    else gated_scan_kernel<T, 128, 8, GS_WHOLE><<<grid, GS_THREADS, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+template <typename T, int MODE>
+static void launch_gated_scan_chunks(const GatedScanArgs& a, int chunks, cudaStream_t st) {
+    dim3 grid(a.B * a.H, (a.e + a.ones + GS_THREADS - 1) / GS_THREADS * a.key_blocks, chunks);
+    if (a.d <= 32) gated_scan_kernel<T, 32, 16, MODE><<<grid, GS_THREADS, 0, st>>>(a);
+    else if (a.d <= 64) gated_scan_kernel<T, 64, 16, MODE><<<grid, GS_THREADS, 0, st>>>(a);
+    else gated_scan_kernel<T, 128, 8, MODE><<<grid, GS_THREADS, 0, st>>>(a);
+}
+
+// long prompts: chunk-local states, decay products, the walk over the chunks, then the outputs from each chunk's start state
+template <typename T>
+static cudaError_t launch_gated_scan_chunked(const GatedScanArgs& a, int chunks, cudaStream_t st) {
+    launch_gated_scan_chunks<T, GS_LOCAL>(a, chunks, st);
+    chunk_decay_kernel<<<dim3(a.B * a.H, chunks), 128, 0, st>>>(a);
+    const int elems = a.d * (a.e + a.ones);
+    scan_combine_kernel<<<dim3(a.B * a.H, (elems + 255) / 256), 256, 0, st>>>(a, chunks);
+    launch_gated_scan_chunks<T, GS_OUTPUT>(a, chunks, st);
     return cudaGetLastError();
 }
 
@@ -429,13 +448,22 @@ int mbh_kv_scatter(const void* k, const void* v, const void* cache_rows, void* r
 }
 
 int mbh_gated_scan(const void* qab, const void* v, int64_t v_pitch, int64_t v_off, void* state, int64_t state_stride, const void* q_start,
-                   const void* seqpos, const void* slots, void* o32, int64_t B, int64_t H, int64_t d, int64_t e, int ones, int dt, void* stream) {
-    if (B == 0) return 0;
-    if (d > 128) return bad("mbh_gated_scan: key size above 128");
+                   const void* seqpos, const void* slots, void* o32, int64_t T, int64_t B, int64_t H, int64_t d, int64_t e, int ones,
+                   int64_t chunk_len, int64_t chunks, void* scratch, int dt, void* stream) {
+    if (B == 0 || T == 0) return 0;
+    if (d > 2048) return bad("mbh_gated_scan: key size above 2048");
+    if (chunks > 1 && (chunk_len < 1 || !scratch || chunks > 65535)) return bad("mbh_gated_scan: chunks need a length and scratch");
+    const int ec = (int)e + (ones ? 1 : 0);
     GatedScanArgs a{(const float*)qab, v, (int)v_pitch, (int)v_off, (float*)state, (int)state_stride, (const int*)q_start, (const int*)seqpos,
-                    (const int*)slots, (float*)o32, (int)B, (int)H, (int)d, (int)e, ones ? 1 : 0};
+                    (const int*)slots, (float*)o32, (int)B, (int)H, (int)d, (int)e, ones ? 1 : 0, (int)chunk_len, (float*)scratch,
+                    scratch ? (float*)scratch + (size_t)B * H * chunks * d * ec : nullptr, (int)((d + 127) / 128)};
     cudaError_t err = cudaSuccess;
-    DISPATCH(dt, err = launch_gated_scan<ST>(a, (cudaStream_t)stream));
+    if (a.key_blocks > 1) {  // the key blocks' CTAs add their partial outputs
+        err = cudaMemsetAsync(o32, 0, sizeof(float) * (size_t)T * H * ec, (cudaStream_t)stream);
+        if (err) return fail(err, "mbh_gated_scan");
+    }
+    if (chunks > 1) DISPATCH(dt, err = launch_gated_scan_chunked<ST>(a, (int)chunks, (cudaStream_t)stream));
+    else DISPATCH(dt, err = launch_gated_scan<ST>(a, (cudaStream_t)stream));
     return err ? fail(err, "mbh_gated_scan") : 0;
 }
 

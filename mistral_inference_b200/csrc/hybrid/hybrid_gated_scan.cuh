@@ -6,6 +6,11 @@
 //
 //   gated_scan       the recurrence; with `ones` the state has one more column whose value is 1 for every token, which carries the
 //                    normaliser n_t = a_t n_(t-1) + b_t, and o has its n_t . q_t in that column
+//                    Long prompts run chunk-parallel, still exactly this recurrence in fp32: every chunk of `chunk_len` tokens first
+//                    runs from a zero state (GS_LOCAL: its own contribution L_c), chunk_decay multiplies each channel's a_t over the
+//                    chunk (A_c), scan_combine walks the chunks in order, S_c = A_c S_(c-1) + L_c, leaving each chunk's START state
+//                    in the scratch and the last one in the cache, and the chunks then run again from their start states for the
+//                    outputs (GS_OUTPUT).  Twice the arithmetic on chunk-count times the CTAs.
 //   hgrn2_gates      f = l + (1 - l) sigmoid(f_pre): a = f, b = 1 - f (the forget gate also decides what is written)
 //   mlstm_m / mlstm_qab   exponential input and forget gates kept in range by a running maximum m (m_0 = 0):
 //                    i = cap tanh(i_pre / cap), f = logsigmoid(cap tanh(f_pre / cap)), m_t = max(f + m_(t-1), i),
@@ -30,36 +35,50 @@ struct GatedScanArgs {
     const int* slots;      // [B]
     float* o;              // [T, H * (e + ones)]
     int B, H, d, e, ones;
+    int chunk_len;         // chunk-parallel modes: tokens per chunk (blockIdx.z is the chunk); whole mode: unused
+    float* scratch;        // [B*H, chunks, d, e + ones] chunk-local states, then chunk start states
+    float* aprod;          // [B*H, chunks, d] product of a_t over each chunk
+    int key_blocks;        // key sizes above 128: the keys are split into blocks of 128 over CTAs (grid.y = column blocks * key_blocks),
+                           // whose partial outputs are summed into a zeroed o with atomic adds
 };
+
+enum { GS_WHOLE = 0, GS_LOCAL = 1, GS_OUTPUT = 2 };
 
 constexpr int GS_THREADS = 128;
 
 // One CTA per (sequence, head, block of GS_THREADS state columns); thread c owns column c of the state in DMAX registers.
 // q, a, b of GS_TB tokens at a time go through shared memory, the next tile is fetched into registers meanwhile (fewer tokens
 // per tile at the largest key size, where the state alone takes 128 registers).
-template <typename T, int DMAX, int GS_TB>
+template <typename T, int DMAX, int GS_TB, int MODE>
 __global__ void __launch_bounds__(GS_THREADS) gated_scan_kernel(GatedScanArgs p) {
     constexpr int R = 3 * GS_TB * DMAX / GS_THREADS;
     __shared__ __align__(16) float qs[GS_TB][DMAX], as[GS_TB][DMAX], bs[GS_TB][DMAX];
     const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
-    const int c = blockIdx.y * GS_THREADS + threadIdx.x;
+    const int ncb = gridDim.y / p.key_blocks, i0 = (blockIdx.y / ncb) * DMAX;  // this CTA's keys: i0 .. i0 + DMAX - 1
+    const int c = (blockIdx.y % ncb) * GS_THREADS + threadIdx.x;
     const int ec = p.e + p.ones;
     const bool live = c < ec, is_one = c >= p.e;
-    const int t0 = p.q_start[b], t1 = p.q_start[b + 1];
+    int t0 = p.q_start[b], t1 = p.q_start[b + 1];
     const int Hd = p.H * p.d;
     float* st = p.state + (size_t)p.slots[b] * p.state_stride + (size_t)h * p.d * ec;
+    if (MODE != GS_WHOLE) {  // this CTA's chunk of the sequence; its state lives in the scratch
+        t0 += blockIdx.z * p.chunk_len;
+        t1 = min(t1, t0 + p.chunk_len);
+        if (t0 >= t1) return;
+        st = p.scratch + ((size_t)blockIdx.x * gridDim.z + blockIdx.z) * p.d * ec;
+    }
     float S[DMAX], pre[R];
-    const bool fresh = p.seqpos[b] == 0;
+    const bool fresh = MODE == GS_LOCAL || (MODE == GS_WHOLE && p.seqpos[b] == 0);
 #pragma unroll
-    for (int i = 0; i < DMAX; ++i) S[i] = (live && !fresh && i < p.d) ? st[(size_t)i * ec + c] : 0.f;
+    for (int i = 0; i < DMAX; ++i) S[i] = (live && !fresh && i0 + i < p.d) ? st[(size_t)(i0 + i) * ec + c] : 0.f;
 
     auto fetch = [&](int tb) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const int idx = threadIdx.x + r * GS_THREADS;
             const int tt = idx / (3 * DMAX), rem = idx % (3 * DMAX), which = rem / DMAX, i = rem % DMAX;
-            const bool ok = tb + tt < t1 && i < p.d;
-            pre[r] = ok ? p.qab[((size_t)(tb + tt) * 3 + which) * Hd + h * p.d + i] : 0.f;
+            const bool ok = tb + tt < t1 && i0 + i < p.d;
+            pre[r] = ok ? p.qab[((size_t)(tb + tt) * 3 + which) * Hd + h * p.d + i0 + i] : 0.f;
         }
     };
     fetch(t0);
@@ -91,15 +110,56 @@ __global__ void __launch_bounds__(GS_THREADS) gated_scan_kernel(GatedScanArgs p)
                     S[i + 2] = fmaf(a4.z, S[i + 2], b4.z * v); o2 = fmaf(S[i + 2], q4.z, o2);
                     S[i + 3] = fmaf(a4.w, S[i + 3], b4.w * v); o3 = fmaf(S[i + 3], q4.w, o3);
                 }
-                p.o[(size_t)(tb + tt) * p.H * ec + h * ec + c] = (o0 + o1) + (o2 + o3);
+                if (MODE != GS_LOCAL) {
+                    float* dst = &p.o[(size_t)(tb + tt) * p.H * ec + h * ec + c];
+                    if (p.key_blocks > 1) atomicAdd(dst, (o0 + o1) + (o2 + o3));
+                    else *dst = (o0 + o1) + (o2 + o3);
+                }
             }
         }
     }
-    if (live) {
+    if (live && MODE != GS_OUTPUT) {
 #pragma unroll
         for (int i = 0; i < DMAX; ++i)
-            if (i < p.d) st[(size_t)i * ec + c] = S[i];
+            if (i0 + i < p.d) st[(size_t)(i0 + i) * ec + c] = S[i];
     }
+}
+
+// aprod[(b, h), chunk, i] = product of a_t[h, i] over the chunk's tokens.  grid (B*H, chunks), threads over i
+__global__ void chunk_decay_kernel(GatedScanArgs p) {
+    const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
+    const int t0 = p.q_start[b] + blockIdx.y * p.chunk_len, t1 = min(p.q_start[b + 1], t0 + p.chunk_len);
+    const int Hd = p.H * p.d;
+    for (int i = threadIdx.x; i < p.d; i += blockDim.x) {
+        float a0 = 1.f, a1 = 1.f;
+        int t = t0;
+        for (; t + 1 < t1; t += 2) {
+            a0 *= p.qab[((size_t)t * 3 + 1) * Hd + h * p.d + i];
+            a1 *= p.qab[((size_t)(t + 1) * 3 + 1) * Hd + h * p.d + i];
+        }
+        if (t < t1) a0 *= p.qab[((size_t)t * 3 + 1) * Hd + h * p.d + i];
+        p.aprod[((size_t)blockIdx.x * gridDim.y + blockIdx.y) * p.d + i] = a0 * a1;
+    }
+}
+
+// One thread per state element (i, column): walks the sequence's chunks in order, S <- A_c[i] S + L_c, replacing L_c in the scratch
+// by the state the chunk STARTS from and writing the last state to the cache.  grid (B*H, ceil(d * ec / blockDim)), `chunks` = grid.z
+// of the scan launches
+__global__ void scan_combine_kernel(GatedScanArgs p, int chunks) {
+    const int b = blockIdx.x / p.H, h = blockIdx.x % p.H, ec = p.e + p.ones;
+    const int idx = blockIdx.y * blockDim.x + threadIdx.x;
+    if (idx >= p.d * ec) return;
+    const int i = idx / ec;
+    const int len = p.q_start[b + 1] - p.q_start[b], n = (len + p.chunk_len - 1) / p.chunk_len;
+    float* st = p.state + (size_t)p.slots[b] * p.state_stride + (size_t)h * p.d * ec + idx;
+    float S = p.seqpos[b] == 0 ? 0.f : *st;
+    for (int c = 0; c < n; ++c) {
+        float* L = p.scratch + ((size_t)blockIdx.x * chunks + c) * p.d * ec + idx;
+        const float l = *L;
+        *L = S;
+        S = fmaf(p.aprod[((size_t)blockIdx.x * chunks + c) * p.d + i], S, l);
+    }
+    if (n > 0) *st = S;
 }
 
 // ------------------------------------------------------------------------------------------------ HGRN2 gates

@@ -583,7 +583,7 @@ class Hgrn2Mixer(nn.Module):
         qfv = _h.linear(hn, self.wqfv, self.bqfv, n_act=self.nqk)
         qab = _h.hgrn2_gates(qfv, self.lower, self.nqk)
         o32 = _h.gated_scan(qab, qfv, qfv.shape[1], 2 * self.nqk, view.state, md.q_start, md.seqpos, md.slots, len(md.seqlens), a.heads, a.dim, a.vdim,
-                            ones=False)
+                            ones=False, max_seqlen=md.max_seqlen)
         y = _h.scan_post(o32, None, self.norm, False, None, 0, 0, a.heads, a.vdim, False, self.eps)
         project_out(y, self.wo, x32, post, scale)
 
@@ -672,7 +672,8 @@ class MlstmMixer(nn.Module):
         qkvg = _h.linear(hn, self.wqkvg)
         gif = _h.linear(hn, self.wif, self.bif, epi=_h.EPI_F32)
         gates, qab = _h.mlstm_gates(qkvg, gif, view.state, self.m_off, md.q_start, md.seqpos, md.slots, B, a.heads, a.dim, a.gate_cap, a.dim ** -0.5)
-        o32 = _h.gated_scan(qab, qkvg, qkvg.shape[1], 2 * self.nqk, view.state, md.q_start, md.seqpos, md.slots, B, a.heads, a.dim, a.vdim, ones=True)
+        o32 = _h.gated_scan(qab, qkvg, qkvg.shape[1], 2 * self.nqk, view.state, md.q_start, md.seqpos, md.slots, B, a.heads, a.dim, a.vdim, ones=True,
+                            max_seqlen=md.max_seqlen)
         y = _h.scan_post(o32, gates, self.norm, True, qkvg, qkvg.shape[1], 2 * self.nqk + self.nv, a.heads, a.vdim, True, self.eps)
         project_out(y, self.wo, x32, post, scale)
 

@@ -148,6 +148,8 @@ MIXER_LAYERS = {
     "both": side_cfg(),
     "matrix_memory": mlstm_cfg(),
     "matrix_memory_2": mlstm_cfg(2, 36, 130, 3.0, "mlstm_2"),
+    "matrix_memory_keys": mlstm_cfg(2, 200, 24, 6.0),          # more keys than one CTA's registers hold: split over CTAs
+    "recurrence_keys": side_cfg(right={"heads": 1, "dim": 260, "vdim": 20}, left_scale=0.0),
 }
 
 
@@ -168,6 +170,39 @@ def test_mixer_alone(tmp_path, dtype, kind):
             pieces.append(toks[o:o + c]); o += c
         _run(m, pieces, taps=taps)
         _close(torch.cat(taps[0]), ref[0], dtype, f"{kind} cut {cuts[:6]}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kind", ["recurrence", "recurrence_wide", "matrix_memory", "matrix_memory_2", "both", "matrix_memory_keys"])
+@pytest.mark.parametrize("chunk", [4, 16, 37])
+def test_chunk_parallel_scan(tmp_path, monkeypatch, dtype, kind, chunk):
+    """The chunk-parallel form of the scan (long prompts) with small chunks: whole prompts whose length is no multiple of the chunk,
+    a second portion that starts from a carried state, a ragged batch in which one sequence is shorter than a chunk."""
+    from mistral_inference_b200 import _abi_hybrid as h
+
+    monkeypatch.setattr(h, "SCAN_CHUNK", chunk)
+    monkeypatch.setattr(h, "SCAN_CHUNK_FROM", chunk + 1)
+    cfg = make_config(width=48, layers=[(MIXER_LAYERS[kind], None)])
+    m, cfg, w = _model(tmp_path, cfg, dtype, seed=11)
+    toks = _tokens(cfg, 90, 1)
+    ref = []
+    O.forward(cfg, w, toks, ref)
+    for cuts in ([90], [41, 49], [3, 86, 1]):
+        taps, o, pieces = {}, 0, []
+        for c in cuts:
+            pieces.append(toks[o:o + c]); o += c
+        _run(m, pieces, taps=taps)
+        _close(torch.cat(taps[0]), ref[0], dtype, f"{kind} chunk {chunk} cut {cuts}")
+    reqs = [_tokens(cfg, n, 20 + n) for n in (70, 3, 55)]
+    cache = m.make_cache(3, 80)
+    lg = m.forward(torch.tensor([t for r in reqs for t in r], device=DEV), [len(r) for r in reqs], cache)
+    o = 0
+    for r in reqs:
+        _close(lg[o:o + len(r)], O.forward(cfg, w, r), dtype, f"{kind} chunk {chunk} in a batch")
+        o += len(r)
+    nxt = m.forward(torch.tensor([1, 2, 3], device=DEV), [1, 1, 1], cache)  # the states the chunked prompt left
+    for i, r in enumerate(reqs):
+        _close(nxt[i], O.forward(cfg, w, r + [i + 1])[-1], dtype, f"{kind} chunk {chunk}: next token of {i}")
 
 
 # ----------------------------------------------------------------------------- whole models
@@ -273,7 +308,7 @@ def test_long_memory_and_long_decoding(tmp_path, dtype):
     assert (ref[-1] - other[-1]).abs().max() > 1e-2, "the first tokens must still show at the end"
     got = _run(m, [toks[:200]] + [[t] for t in toks[200:]])
     _close(got, ref, dtype, "long", tol=1e-3)
-    _close(_run(m, [toks]), ref, dtype, "long prompt", tol=1e-3)
+    _close(_run(m, [toks]), ref, dtype, "long prompt (chunk-parallel scan)", tol=1e-3)
 
 
 def test_first_tokens_and_rows_far_apart(tmp_path):
