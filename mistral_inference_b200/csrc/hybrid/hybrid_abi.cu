@@ -72,7 +72,8 @@ static cudaError_t launch_gated_scan_chunked(const GatedScanArgs& a, int chunks,
 
 template <typename T> static void run_mlstm_gates(const MlstmGateArgs& a, int64_t B, int64_t T_, cudaStream_t st) {
     mlstm_m_kernel<T><<<(unsigned)(B * a.H), 32, 0, st>>>(a);
-    mlstm_qab_kernel<T><<<(unsigned)T_, 128, 0, st>>>(a);
+    const unsigned jb = T_ < 512 ? (unsigned)((a.H * a.d + 255) / 256) : 1u;
+    mlstm_qab_kernel<T><<<dim3((unsigned)T_, jb), 256, 0, st>>>(a);
 }
 template <typename T> static void run_embed(const void* tokens, const void* table, float scale, void* x32, int64_t T_, int64_t D, cudaStream_t st) {
     embed_scale_kernel<T><<<(unsigned)T_, 128, 0, st>>>((const int64_t*)tokens, (const T*)table, scale, (float*)x32, (int)D);
@@ -432,7 +433,9 @@ int mbh_rot_prep(const void* qkv, const void* freq, const void* positions, const
     RotPrepArgs a{qkv, (const double*)freq, (const int*)positions, (const int*)cache_rows, q_out, k_out, v_out, ring_k, ring_v,
                   (int)H, (int)G, (int)d, (int)e, (int)rot_dims, unit_norm, eps};
     cudaStream_t st = (cudaStream_t)stream;
-    DISPATCH(dt, rot_prep_kernel<ST><<<(unsigned)T, 128, 0, st>>>(a));
+    // few tokens (decode): the heads of a token are spread over CTAs; prompts: one CTA per token
+    const unsigned hb = T < 512 ? (unsigned)((H + G + 3) / 4) : 1u;
+    DISPATCH(dt, rot_prep_kernel<ST><<<dim3((unsigned)T, hb), 128, 0, st>>>(a));
     cudaError_t err = cudaGetLastError();
     return err ? fail(err, "mbh_rot_prep") : 0;
 }
@@ -471,7 +474,8 @@ int mbh_hgrn2_gates(const void* qfv, const void* lower, void* qab, int64_t T, in
     if (T == 0) return 0;
     Hgrn2GateArgs a{qfv, lower, (float*)qab, (int)Hd, (int)pitch};
     cudaStream_t st = (cudaStream_t)stream;
-    DISPATCH(dt, hgrn2_gates_kernel<ST><<<(unsigned)T, 128, 0, st>>>(a));
+    const unsigned jb = T < 512 ? (unsigned)((Hd + 255) / 256) : 1u;
+    DISPATCH(dt, hgrn2_gates_kernel<ST><<<dim3((unsigned)T, jb), 256, 0, st>>>(a));
     cudaError_t err = cudaGetLastError();
     return err ? fail(err, "mbh_hgrn2_gates") : 0;
 }
@@ -494,7 +498,8 @@ int mbh_scan_post(const void* o32, const void* gates, const void* w, int w_per_h
     if (ones && !gates) return bad("mbh_scan_post: a normaliser column needs the gates");
     ScanPostArgs a{(const float*)o32, (const float*)gates, w, w_per_head, gate, (int)g_pitch, (int)g_off, y, (int)H, (int)e, ones ? 1 : 0, eps};
     cudaStream_t st = (cudaStream_t)stream;
-    DISPATCH(dt, scan_post_kernel<ST><<<(unsigned)T, 128, 0, st>>>(a));
+    const unsigned hb = T < 512 ? (unsigned)((H + 3) / 4) : 1u;
+    DISPATCH(dt, scan_post_kernel<ST><<<dim3((unsigned)T, hb), 128, 0, st>>>(a));
     cudaError_t err = cudaGetLastError();
     return err ? fail(err, "mbh_scan_post") : 0;
 }

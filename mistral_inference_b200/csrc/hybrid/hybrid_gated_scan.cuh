@@ -172,10 +172,10 @@ struct Hgrn2GateArgs {
 
 template <typename T>
 __global__ void hgrn2_gates_kernel(Hgrn2GateArgs p) {
-    const int t = blockIdx.x;
+    const int t = blockIdx.x;  // grid (T, blocks of blockDim entries): a decode step has few tokens but thousands of entries
     const T* row = static_cast<const T*>(p.qfv) + (size_t)t * p.pitch;
     float* out = p.qab + (size_t)t * 3 * p.Hd;
-    for (int j = threadIdx.x; j < p.Hd; j += blockDim.x) {
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < p.Hd; j += gridDim.y * blockDim.x) {
         const float l = to_f(static_cast<const T*>(p.lower)[j]);
         const float f = l + (1.f - l) * sigmoid_exact(to_f(row[p.Hd + j]));
         out[j] = to_f(row[j]);
@@ -237,7 +237,7 @@ __global__ void mlstm_qab_kernel(MlstmGateArgs p) {
     const int t = blockIdx.x, Hd = p.H * p.d;
     const T* row = static_cast<const T*>(p.qkvg) + (size_t)t * p.pitch;
     float* out = p.qab + (size_t)t * 3 * Hd;
-    for (int j = threadIdx.x; j < Hd; j += blockDim.x) {
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < Hd; j += gridDim.y * blockDim.x) {
         const float* g = p.gates + ((size_t)t * p.H + j / p.d) * 3;
         out[j] = to_f(row[j]) * p.qscale;
         out[Hd + j] = g[0];
@@ -258,12 +258,12 @@ struct ScanPostArgs {
     float eps;
 };
 
-// one CTA per token, a warp per head
+// grid (T, groups of heads), a warp per head
 template <typename T>
 __global__ void __launch_bounds__(128) scan_post_kernel(ScanPostArgs p) {
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int ec = p.e + p.ones;
-    for (int h = warp; h < p.H; h += nw) {
+    for (int h = blockIdx.y * nw + warp; h < p.H; h += gridDim.y * nw) {
         const float* o = p.o + ((size_t)t * p.H + h) * ec;
         float den = 1.f;
         if (p.ones) den = fmaxf(fabsf(o[p.e]), p.gates[((size_t)t * p.H + h) * 3 + 2]) + 1e-6f;

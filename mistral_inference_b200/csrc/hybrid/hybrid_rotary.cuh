@@ -37,7 +37,7 @@ struct RotPrepArgs {
 
 constexpr int RP_MAXP = 4;  // pairs per lane: head sizes up to 256
 
-// one CTA per token, a warp per head
+// grid (T, groups of heads), a warp per head
 template <typename T>
 __global__ void __launch_bounds__(128) rot_prep_kernel(RotPrepArgs a) {
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(128) rot_prep_kernel(RotPrepArgs a) {
     const int pos = a.positions[t];
     const int crow = a.cache_rows ? a.cache_rows[t] : -1;
     const int half = a.d >> 1;  // pairs; an odd last entry passes unchanged
-    for (int h = warp; h < a.H + a.G; h += nw) {
+    for (int h = blockIdx.y * nw + warp; h < a.H + a.G; h += gridDim.y * nw) {
         const bool is_q = h < a.H;
         const T* src = row + (is_q ? h * a.d : Nq + (h - a.H) * a.d);
         float u[RP_MAXP], v[RP_MAXP], ss = 0.f;
@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(128) rot_prep_kernel(RotPrepArgs a) {
         }
     }
     const T* vsrc = row + Nq + Nk;
-    for (int i = threadIdx.x; i < Nv; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < Nv; i += gridDim.y * blockDim.x) {
         if (a.v_out) static_cast<T*>(a.v_out)[(size_t)t * Nv + i] = vsrc[i];
         if (crow >= 0) static_cast<T*>(a.ring_v)[(size_t)crow * Nv + i] = vsrc[i];
     }
