@@ -472,9 +472,9 @@ def lotazen_kernel_table(s: dict, T: int, ctx: int, peaks: dict, dev) -> dict:
     rec("gated_scan prompt (mLSTM, normaliser column), chunk-parallel",
         _time(lambda: h.gated_scan(qab2, qkvg, 4 * Hd, 2 * Hd, mstate, md.q_start, zero, md.slots, 1, RH, d, d, ones=True, max_seqlen=T), 2, 5, flush),
         flops=4.0 * T * RH * d * (d + 1))
-    om = h.gated_scan(qab2, qkvg, 4 * Hd, 2 * Hd, mstate, md.q_start, zero, md.slots, 1, RH, d, d, ones=True)
+    om, nq = h.gated_scan(qab2, qkvg, 4 * Hd, 2 * Hd, mstate, md.q_start, zero, md.slots, 1, RH, d, d, ones=True)
     nw = torch.ones(Hd, device=dev).to(bf)
-    rec("scan_post prompt (mLSTM)", _time(lambda: h.scan_post(om, gates, nw, True, qkvg, 4 * Hd, 3 * Hd, RH, d, True, 1e-5), 3, 8, flush), bytes_=T * Hd * (4 + 2 + 2.0))
+    rec("scan_post prompt (mLSTM)", _time(lambda: h.scan_post(om, gates, nw, True, qkvg, 4 * Hd, 3 * Hd, RH, d, True, 1e-5, nq=nq), 3, 8, flush), bytes_=T * Hd * (4 + 4 + 2 + 2.0))
     rec("like: gated_headnorm prompt", _time(lambda: h.gated_headnorm(o32, nw, qkvg, 4 * Hd, 3 * Hd, 1e-5), 3, 8, flush), bytes_=T * Hd * (4 + 2 + 2.0))
     one = torch.ones(B, dtype=torch.int32, device=dev)
     qabB = qab[:B].contiguous()

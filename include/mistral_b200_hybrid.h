@@ -127,9 +127,10 @@ int mbh_moe_route(const void* h, const void* w_router, const void* correction, v
 /* The chosen experts of few tokens: y32 [T, width] = sum_k wsel[t, k] * expert(idx[t, k])(h[t]); an index >= E is an identity
  * expert (output = h[t]).  w13 [E * 2 * ff, width] (gate and up rows interleaved), w2 [width, E * ff]; act: scratch [T * top, ff].
  * glu 0: experts silu(gate) * up.  glu 1: the weight multiplies the expert's INPUT and the unit is the clamped one of mbh_linear's
- * epilogue 2: y32 = sum_k expert(wsel[t, k] * h[t]), g = min(w gate, limit), u = clamp(w up, -limit, limit). */
+ * epilogue 2: y32 = sum_k expert(wsel[t, k] * h[t]), g = min(w gate, limit), u = clamp(w up, -limit, limit).
+ * accumulate 1: the sum is ADDED to y32 (the fp32 residual stream) instead of stored. */
 int mbh_moe_sparse(const void* h, const void* w13, const void* w2, const void* idx, const void* wsel, void* act, void* y32, int64_t T, int64_t width,
-                   int64_t ff, int64_t E, int64_t top, int glu, float limit, float alpha, int dt, void* stream);
+                   int64_t ff, int64_t E, int64_t top, int glu, float limit, float alpha, int accumulate, int dt, void* stream);
 
 /* y32[t, :] += (dense[t, first] + ... + dense[t, n - 1]) * h[t, :]. */
 int mbh_rows_axpy(void* y32, const void* h, const void* dense, int64_t T, int64_t n, int64_t first, int64_t D, int dt, void* stream);
@@ -167,14 +168,14 @@ int mbh_kv_scatter(const void* k, const void* v, const void* cache_rows, void* r
 
 /* Gated linear recurrence per head: S <- diag(a_t) S + b_t v_t^T, o_t = S^T q_t.  qab fp32 [T, 3, H*d] = q | a | b; value (t, h, c) at
  * v[t * v_pitch + v_off + h*e + c] (storage type); state fp32 [slots, state_stride], head h's matrix [d, e + ones] at h * d * (e + ones),
- * read (unless seqpos[b] == 0: zero) and written back; o32 fp32 [T, H * (e + ones)].  ones = 1: one more state column whose value is 1
- * for every token (a normaliser n <- a n + b; o32 has n . q there).
+ * read (unless seqpos[b] == 0: zero) and written back; o32 fp32 [T, H * e].  ones = 1: one more state column whose value is 1 for every
+ * token (a normaliser n <- a n + b); nq fp32 [T, H * d] gets n_t[i] * q_t[i] (summed over d by mbh_scan_post); ones = 0: nq null.
  * chunks > 1 (long prompts): the same recurrence chunk-parallel, `chunks` = ceil(longest sequence / chunk_len) chunks of chunk_len
  * tokens per sequence; scratch: fp32 [B*H*chunks*d*(e + ones + 1)].  chunks <= 1: one CTA column walks each sequence; no scratch.
  * Key sizes above 128 are split into blocks of 128 keys over CTAs that add their partial outputs into o32 (T tokens, zeroed first). */
 int mbh_gated_scan(const void* qab, const void* v, int64_t v_pitch, int64_t v_off, void* state, int64_t state_stride, const void* q_start,
-                   const void* seqpos, const void* slots, void* o32, int64_t T, int64_t B, int64_t H, int64_t d, int64_t e, int ones,
-                   int64_t chunk_len, int64_t chunks, void* scratch, int dt, void* stream);
+                   const void* seqpos, const void* slots, void* o32, void* nq, int64_t T, int64_t B, int64_t H, int64_t d, int64_t e,
+                   int ones, int64_t chunk_len, int64_t chunks, void* scratch, int dt, void* stream);
 
 /* HGRN2 gates from qfv [T, pitch] = silu(q) | f_pre | v: f = lower + (1 - lower) * sigmoid(f_pre); qab [T, 3, Hd] = q | f | 1 - f. */
 int mbh_hgrn2_gates(const void* qfv, const void* lower, void* qab, int64_t T, int64_t Hd, int64_t pitch, int dt, void* stream);
@@ -187,10 +188,10 @@ int mbh_mlstm_gates(const void* qkvg, const void* gif, void* gates, void* qab, v
                     const void* seqpos, const void* slots, int64_t T, int64_t B, int64_t H, int64_t d, int64_t pitch, float cap, float qscale, int dt,
                     void* stream);
 
-/* After a scan: o = o32[t, h, :e] (divided by max(|o32[t, h, e]|, gates[t, h, 2]) + 1e-6 with ones = 1); y = o / sqrt(mean(o^2) + eps) * w
+/* After a scan: o = o32[t, h, :e] (divided by max(|sum_i nq[t, h, i]|, gates[t, h, 2]) + 1e-6 with ones = 1; nq [T, H * d]); y = o / sqrt(mean(o^2) + eps) * w
  * (w [H*e] with w_per_head, else [e] shared by the heads) * sigmoid(gate[t * g_pitch + g_off + h*e + c]) (gate null: none).  y [T, H*e]. */
-int mbh_scan_post(const void* o32, const void* gates, const void* w, int w_per_head, const void* gate, int64_t g_pitch, int64_t g_off, void* y,
-                  int64_t T, int64_t H, int64_t e, int ones, float eps, int dt, void* stream);
+int mbh_scan_post(const void* o32, const void* nq, int64_t d, const void* gates, const void* w, int w_per_head, const void* gate, int64_t g_pitch,
+                  int64_t g_off, void* y, int64_t T, int64_t H, int64_t e, int ones, float eps, int dt, void* stream);
 
 #ifdef __cplusplus
 }

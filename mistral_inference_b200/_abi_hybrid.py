@@ -42,17 +42,17 @@ _SIGNATURES = {
     "mbh_attn_latent_decode": (c_int, [P, P, P, P, P, I, I, I, I, I, F, I, P, c_int, P]),
     "mbh_latent_vup": (c_int, [P, P, P, I, I, P, I, I, I, I, c_int, P]),
     "mbh_moe_route": (c_int, [P, P, P, P, P, P, I, I, I, I, I, I, c_int, c_int, P]),
-    "mbh_moe_sparse": (c_int, [P, P, P, P, P, P, P, I, I, I, I, I, c_int, F, F, c_int, P]),
+    "mbh_moe_sparse": (c_int, [P, P, P, P, P, P, P, I, I, I, I, I, c_int, F, F, c_int, c_int, P]),
     "mbh_attn_window": (c_int, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, I, P, P, P, c_int, P]),
     "mbh_linear_glu": (c_int, [P, P, P, I, I, I, F, F, P, I, I, c_int, P]),
     "mbh_glu_epilogue": (c_int, [P, P, I, I, F, F, P, I, I, c_int, P]),
     "mbh_embed_pos": (c_int, [P, P, P, P, F, P, I, I, c_int, P]),
     "mbh_rot_prep": (c_int, [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, c_int, F, c_int, P]),
     "mbh_kv_scatter": (c_int, [P, P, P, P, P, I, I, I, c_int, P]),
-    "mbh_gated_scan": (c_int, [P, P, I, I, P, I, P, P, P, P, I, I, I, I, I, c_int, I, I, P, c_int, P]),
+    "mbh_gated_scan": (c_int, [P, P, I, I, P, I, P, P, P, P, P, I, I, I, I, I, c_int, I, I, P, c_int, P]),
     "mbh_hgrn2_gates": (c_int, [P, P, P, I, I, I, c_int, P]),
     "mbh_mlstm_gates": (c_int, [P, P, P, P, P, I, I, P, P, P, I, I, I, I, I, F, F, c_int, P]),
-    "mbh_scan_post": (c_int, [P, P, P, c_int, P, I, I, P, I, I, I, c_int, F, c_int, P]),
+    "mbh_scan_post": (c_int, [P, P, I, P, P, c_int, P, I, I, P, I, I, I, c_int, F, c_int, P]),
     "mbh_rows_axpy": (c_int, [P, P, P, I, I, I, I, c_int, P]),
 }
 
@@ -245,15 +245,18 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
 
 
 def moe_sparse(h: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, idx: torch.Tensor, wsel: torch.Tensor, E: int, ff: int,
-               glu: bool = False, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
+               glu: bool = False, limit: float = 0.0, alpha: float = 0.0, add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
     """fp32 [T, width]: the weighted sum of each token's chosen experts (indices >= E: identity), streaming only their weights.
-    glu: clamped gated experts whose INPUT is multiplied by the routing weight."""
+    glu: clamped gated experts whose INPUT is multiplied by the routing weight.  add_to (fp32 [T, width], the residual stream): the
+    sum is added to it in place instead of returned in a new tensor."""
     T, D = h.shape
     top = idx.shape[1]
     act = torch.empty(T * top, ff, dtype=h.dtype, device=h.device)
-    y32 = torch.empty(T, D, dtype=torch.float32, device=h.device)
+    if add_to is not None:
+        assert add_to.dtype == torch.float32 and add_to.shape == (T, D)
+    y32 = torch.empty(T, D, dtype=torch.float32, device=h.device) if add_to is None else add_to
     _check(lib().mbh_moe_sparse(_ptr(h), _ptr(w13), _ptr(w2), _ptr(idx), _ptr(wsel), _ptr(act), _ptr(y32), T, D, ff, E, top, int(glu), limit, alpha,
-                                dt_of(h.dtype), _stream()), "mbh_moe_sparse")
+                                int(add_to is not None), dt_of(h.dtype), _stream()), "mbh_moe_sparse")
     return y32
 
 
@@ -385,20 +388,22 @@ SCAN_CHUNK_FROM = 512  # sequences (portions) at least this long run chunk-paral
 
 
 def gated_scan(qab, v, v_pitch: int, v_off: int, state, q_start, seqpos, slots, B: int, H: int, d: int, e: int, ones: bool,
-               max_seqlen: int = 0) -> torch.Tensor:
-    """fp32 [T, H * (e + ones)] of S <- diag(a) S + b v^T, o = S^T q; the state rows of `slots` are read and written.  With the
-    longest sequence of the call given and at least SCAN_CHUNK_FROM, the scan runs chunk-parallel (same recurrence, fp32)."""
+               max_seqlen: int = 0):
+    """fp32 o [T, H * e] of S <- diag(a) S + b v^T, o = S^T q; the state rows of `slots` are read and written.  With `ones` the state
+    has a normaliser column and the result is (o, nq [T, H * d]) for `scan_post`.  With the longest sequence of the call given and at
+    least SCAN_CHUNK_FROM, the scan runs chunk-parallel (same recurrence, fp32)."""
     assert qab.dtype == torch.float32 and state.dtype == torch.float32
     T = qab.shape[0]
     ec = e + int(ones)
-    o = torch.empty(T, H * ec, dtype=torch.float32, device=qab.device)
+    o = torch.empty(T, H * e, dtype=torch.float32, device=qab.device)
+    nq = torch.empty(T, H * d, dtype=torch.float32, device=qab.device) if ones else None
     chunks, scratch = 1, None
     if max_seqlen >= SCAN_CHUNK_FROM and max_seqlen > SCAN_CHUNK:
         chunks = (max_seqlen + SCAN_CHUNK - 1) // SCAN_CHUNK
         scratch = torch.empty(B * H * chunks * d * (ec + 1), dtype=torch.float32, device=qab.device)
-    _check(lib().mbh_gated_scan(_ptr(qab), _ptr(v), v_pitch, v_off, _ptr(state), state[0].numel(), _ptr(q_start), _ptr(seqpos), _ptr(slots), _ptr(o), T, B, H, d,
-                                e, int(ones), SCAN_CHUNK, chunks, _ptr(scratch), dt_of(v.dtype), _stream()), "mbh_gated_scan")
-    return o
+    _check(lib().mbh_gated_scan(_ptr(qab), _ptr(v), v_pitch, v_off, _ptr(state), state[0].numel(), _ptr(q_start), _ptr(seqpos), _ptr(slots), _ptr(o), _ptr(nq), T, B, H,
+                                d, e, int(ones), SCAN_CHUNK, chunks, _ptr(scratch), dt_of(v.dtype), _stream()), "mbh_gated_scan")
+    return (o, nq) if ones else o
 
 
 def hgrn2_gates(qfv, lower, Hd: int) -> torch.Tensor:
@@ -418,10 +423,10 @@ def mlstm_gates(qkvg, gif, state, m_off: int, q_start, seqpos, slots, B: int, H:
     return gates, qab
 
 
-def scan_post(o32, gates, w, w_per_head: bool, gate, g_pitch: int, g_off: int, H: int, e: int, ones: bool, eps: float) -> torch.Tensor:
+def scan_post(o32, gates, w, w_per_head: bool, gate, g_pitch: int, g_off: int, H: int, e: int, ones: bool, eps: float, nq=None) -> torch.Tensor:
     T = o32.shape[0]
     y = torch.empty(T, H * e, dtype=w.dtype, device=o32.device)
-    _check(lib().mbh_scan_post(_ptr(o32), _ptr(gates), _ptr(w), int(w_per_head), _ptr(gate), g_pitch, g_off, _ptr(y), T, H, e, int(ones), eps,
+    _check(lib().mbh_scan_post(_ptr(o32), _ptr(nq), nq.shape[1] // H if nq is not None else 0, _ptr(gates), _ptr(w), int(w_per_head), _ptr(gate), g_pitch, g_off, _ptr(y), T, H, e, int(ones), eps,
                                dt_of(w.dtype), _stream()), "mbh_scan_post")
     return y
 

@@ -42,21 +42,33 @@ static cudaError_t launch_lightning(const LightningArgs& a, cudaStream_t st) {
 }
 
 
+// key size -> registers per state column; tokens per shared-memory tile chosen so that nothing spills
+template <typename T, int MODE>
+static void launch_gated_scan_mode(const GatedScanArgs& a, dim3 grid, cudaStream_t st) {
+    if (a.ones) {
+        if (a.d <= 32) gated_scan_kernel<T, 32, 16, MODE, true><<<grid, GS_THREADS, 0, st>>>(a);
+        else if (a.d <= 64) gated_scan_kernel<T, 64, 16, MODE, true><<<grid, GS_THREADS, 0, st>>>(a);
+        else if (a.d <= 128) gated_scan_kernel<T, 128, 8, MODE, true><<<grid, GS_THREADS, 0, st>>>(a);
+        else gated_scan_kernel<T, 128, 8, MODE, true, true><<<grid, GS_THREADS, 0, st>>>(a);
+    } else {
+        if (a.d <= 32) gated_scan_kernel<T, 32, 16, MODE, false><<<grid, GS_THREADS, 0, st>>>(a);
+        else if (a.d <= 64) gated_scan_kernel<T, 64, 16, MODE, false><<<grid, GS_THREADS, 0, st>>>(a);
+        else if (a.d <= 128) gated_scan_kernel<T, 128, 8, MODE, false><<<grid, GS_THREADS, 0, st>>>(a);
+        else gated_scan_kernel<T, 128, 8, MODE, false, true><<<grid, GS_THREADS, 0, st>>>(a);
+    }
+}
+
 template <typename T>
 static cudaError_t launch_gated_scan(const GatedScanArgs& a, cudaStream_t st) {
-    dim3 grid(a.B * a.H, (a.e + a.ones + GS_THREADS - 1) / GS_THREADS * a.key_blocks);
-    if (a.d <= 32) gated_scan_kernel<T, 32, 16, GS_WHOLE><<<grid, GS_THREADS, 0, st>>>(a);
-    else if (a.d <= 64) gated_scan_kernel<T, 64, 16, GS_WHOLE><<<grid, GS_THREADS, 0, st>>>(a);
-    else gated_scan_kernel<T, 128, 8, GS_WHOLE><<<grid, GS_THREADS, 0, st>>>(a);
+    dim3 grid(a.B * a.H, (a.e + GS_THREADS - 1) / GS_THREADS * a.key_blocks);
+    launch_gated_scan_mode<T, GS_WHOLE>(a, grid, st);
     return cudaGetLastError();
 }
 
 template <typename T, int MODE>
 static void launch_gated_scan_chunks(const GatedScanArgs& a, int chunks, cudaStream_t st) {
-    dim3 grid(a.B * a.H, (a.e + a.ones + GS_THREADS - 1) / GS_THREADS * a.key_blocks, chunks);
-    if (a.d <= 32) gated_scan_kernel<T, 32, 16, MODE><<<grid, GS_THREADS, 0, st>>>(a);
-    else if (a.d <= 64) gated_scan_kernel<T, 64, 16, MODE><<<grid, GS_THREADS, 0, st>>>(a);
-    else gated_scan_kernel<T, 128, 8, MODE><<<grid, GS_THREADS, 0, st>>>(a);
+    dim3 grid(a.B * a.H, (a.e + GS_THREADS - 1) / GS_THREADS * a.key_blocks, chunks);
+    launch_gated_scan_mode<T, MODE>(a, grid, st);
 }
 
 // long prompts: chunk-local states, decay products, the walk over the chunks, then the outputs from each chunk's start state
@@ -374,9 +386,9 @@ int mbh_moe_route(const void* h, const void* w_router, const void* correction, v
 }
 
 int mbh_moe_sparse(const void* h, const void* w13, const void* w2, const void* idx, const void* wsel, void* act, void* y32, int64_t T, int64_t width,
-                   int64_t ff, int64_t E, int64_t top, int glu, float limit, float alpha, int dt, void* stream) {
+                   int64_t ff, int64_t E, int64_t top, int glu, float limit, float alpha, int accumulate, int dt, void* stream) {
     if (T == 0) return 0;
-    MoeSparseArgs a{h, w13, w2, (const int*)idx, (const float*)wsel, act, (float*)y32, (int)width, (int)ff, (int)E, (int)top, glu, limit, alpha};
+    MoeSparseArgs a{h, w13, w2, (const int*)idx, (const float*)wsel, act, (float*)y32, (int)width, (int)ff, (int)E, (int)top, glu, limit, alpha, accumulate};
     cudaStream_t st = (cudaStream_t)stream;
     DISPATCH(dt, run_moe_sparse<ST>(a, T, st));
     cudaError_t e = cudaGetLastError();
@@ -451,18 +463,19 @@ int mbh_kv_scatter(const void* k, const void* v, const void* cache_rows, void* r
 }
 
 int mbh_gated_scan(const void* qab, const void* v, int64_t v_pitch, int64_t v_off, void* state, int64_t state_stride, const void* q_start,
-                   const void* seqpos, const void* slots, void* o32, int64_t T, int64_t B, int64_t H, int64_t d, int64_t e, int ones,
-                   int64_t chunk_len, int64_t chunks, void* scratch, int dt, void* stream) {
+                   const void* seqpos, const void* slots, void* o32, void* nq, int64_t T, int64_t B, int64_t H, int64_t d, int64_t e,
+                   int ones, int64_t chunk_len, int64_t chunks, void* scratch, int dt, void* stream) {
     if (B == 0 || T == 0) return 0;
+    if (!ones != !nq) return bad("mbh_gated_scan: the normaliser column and its output come together");
     if (d > 2048) return bad("mbh_gated_scan: key size above 2048");
     if (chunks > 1 && (chunk_len < 1 || !scratch || chunks > 65535)) return bad("mbh_gated_scan: chunks need a length and scratch");
     const int ec = (int)e + (ones ? 1 : 0);
     GatedScanArgs a{(const float*)qab, v, (int)v_pitch, (int)v_off, (float*)state, (int)state_stride, (const int*)q_start, (const int*)seqpos,
-                    (const int*)slots, (float*)o32, (int)B, (int)H, (int)d, (int)e, ones ? 1 : 0, (int)chunk_len, (float*)scratch,
+                    (const int*)slots, (float*)o32, (float*)nq, (int)B, (int)H, (int)d, (int)e, ones ? 1 : 0, (int)chunk_len, (float*)scratch,
                     scratch ? (float*)scratch + (size_t)B * H * chunks * d * ec : nullptr, (int)((d + 127) / 128)};
     cudaError_t err = cudaSuccess;
     if (a.key_blocks > 1) {  // the key blocks' CTAs add their partial outputs
-        err = cudaMemsetAsync(o32, 0, sizeof(float) * (size_t)T * H * ec, (cudaStream_t)stream);
+        err = cudaMemsetAsync(o32, 0, sizeof(float) * (size_t)T * H * e, (cudaStream_t)stream);
         if (err) return fail(err, "mbh_gated_scan");
     }
     if (chunks > 1) DISPATCH(dt, err = launch_gated_scan_chunked<ST>(a, (int)chunks, (cudaStream_t)stream));
@@ -492,11 +505,11 @@ int mbh_mlstm_gates(const void* qkvg, const void* gif, void* gates, void* qab, v
     return err ? fail(err, "mbh_mlstm_gates") : 0;
 }
 
-int mbh_scan_post(const void* o32, const void* gates, const void* w, int w_per_head, const void* gate, int64_t g_pitch, int64_t g_off, void* y,
-                  int64_t T, int64_t H, int64_t e, int ones, float eps, int dt, void* stream) {
+int mbh_scan_post(const void* o32, const void* nq, int64_t d, const void* gates, const void* w, int w_per_head, const void* gate, int64_t g_pitch,
+                  int64_t g_off, void* y, int64_t T, int64_t H, int64_t e, int ones, float eps, int dt, void* stream) {
     if (T == 0) return 0;
-    if (ones && !gates) return bad("mbh_scan_post: a normaliser column needs the gates");
-    ScanPostArgs a{(const float*)o32, (const float*)gates, w, w_per_head, gate, (int)g_pitch, (int)g_off, y, (int)H, (int)e, ones ? 1 : 0, eps};
+    if (ones && (!gates || !nq)) return bad("mbh_scan_post: a normaliser needs its products and the gates");
+    ScanPostArgs a{(const float*)o32, (const float*)nq, (int)d, (const float*)gates, w, w_per_head, gate, (int)g_pitch, (int)g_off, y, (int)H, (int)e, ones ? 1 : 0, eps};
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned hb = T < 512 ? (unsigned)((H + 3) / 4) : 1u;
     DISPATCH(dt, scan_post_kernel<ST><<<dim3((unsigned)T, hb), 128, 0, st>>>(a));

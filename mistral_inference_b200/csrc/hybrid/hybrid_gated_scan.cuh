@@ -4,8 +4,10 @@
 //
 // and the small kernels that turn a layer's projections into (q, a, b) and its raw output into the next Linear's input.
 //
-//   gated_scan       the recurrence; with `ones` the state has one more column whose value is 1 for every token, which carries the
-//                    normaliser n_t = a_t n_(t-1) + b_t, and o has its n_t . q_t in that column
+//   gated_scan       the recurrence; with `ones` the state has one more column whose value is 1 for every token: the normaliser
+//                    n_t = a_t n_(t-1) + b_t.  It does not get a thread column of its own (at 128 value columns that would be a second
+//                    CTA with one live thread): thread i of the first column block carries n[i] beside its state column and writes
+//                    n_t[i] q_t[i] per token; scan_post sums them to n_t . q_t
 //                    Long prompts run chunk-parallel, still exactly this recurrence in fp32: every chunk of `chunk_len` tokens first
 //                    runs from a zero state (GS_LOCAL: its own contribution L_c), chunk_decay multiplies each channel's a_t over the
 //                    chunk (A_c), scan_combine walks the chunks in order, S_c = A_c S_(c-1) + L_c, leaving each chunk's START state
@@ -33,7 +35,8 @@ struct GatedScanArgs {
     const int* q_start;    // [B + 1]
     const int* seqpos;     // [B] tokens before this call (0: the state starts at zero)
     const int* slots;      // [B]
-    float* o;              // [T, H * (e + ones)]
+    float* o;              // [T, H * e]
+    float* nq;             // with `ones`: [T, H * d], n_t[i] * q_t[i]
     int B, H, d, e, ones;
     int chunk_len;         // chunk-parallel modes: tokens per chunk (blockIdx.z is the chunk); whole mode: unused
     float* scratch;        // [B*H, chunks, d, e + ones] chunk-local states, then chunk start states
@@ -48,16 +51,19 @@ constexpr int GS_THREADS = 128;
 
 // One CTA per (sequence, head, block of GS_THREADS state columns); thread c owns column c of the state in DMAX registers.
 // q, a, b of GS_TB tokens at a time go through shared memory, the next tile is fetched into registers meanwhile (fewer tokens
-// per tile at the largest key size, where the state alone takes 128 registers).
-template <typename T, int DMAX, int GS_TB, int MODE>
+// per tile at the largest key size, where the state alone takes 128 registers, and fewer again with the normaliser).
+template <typename T, int DMAX, int GS_TB, int MODE, bool ONES, bool SPLIT = false>
 __global__ void __launch_bounds__(GS_THREADS) gated_scan_kernel(GatedScanArgs p) {
     constexpr int R = 3 * GS_TB * DMAX / GS_THREADS;
     __shared__ __align__(16) float qs[GS_TB][DMAX], as[GS_TB][DMAX], bs[GS_TB][DMAX];
     const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
-    const int ncb = gridDim.y / p.key_blocks, i0 = (blockIdx.y / ncb) * DMAX;  // this CTA's keys: i0 .. i0 + DMAX - 1
+    // SPLIT (key sizes above DMAX): this CTA's keys are i0 .. i0 + DMAX - 1, its outputs partial sums
+    const int ncb = SPLIT ? gridDim.y / p.key_blocks : gridDim.y, i0 = SPLIT ? (blockIdx.y / ncb) * DMAX : 0;
     const int c = (blockIdx.y % ncb) * GS_THREADS + threadIdx.x;
     const int ec = p.e + p.ones;
-    const bool live = c < ec, is_one = c >= p.e;
+    const bool live = c < p.e;
+    // the normaliser entry this thread carries: key i0 + threadIdx.x, in the first column block only
+    const bool nrm = ONES && (blockIdx.y % ncb) == 0 && threadIdx.x < DMAX && i0 + (int)threadIdx.x < p.d;
     int t0 = p.q_start[b], t1 = p.q_start[b + 1];
     const int Hd = p.H * p.d;
     float* st = p.state + (size_t)p.slots[b] * p.state_stride + (size_t)h * p.d * ec;
@@ -71,6 +77,7 @@ __global__ void __launch_bounds__(GS_THREADS) gated_scan_kernel(GatedScanArgs p)
     const bool fresh = MODE == GS_LOCAL || (MODE == GS_WHOLE && p.seqpos[b] == 0);
 #pragma unroll
     for (int i = 0; i < DMAX; ++i) S[i] = (live && !fresh && i0 + i < p.d) ? st[(size_t)(i0 + i) * ec + c] : 0.f;
+    float nst = (nrm && !fresh) ? st[(size_t)(i0 + threadIdx.x) * ec + p.e] : 0.f;
 
     auto fetch = [&](int tb) {
 #pragma unroll
@@ -82,7 +89,7 @@ __global__ void __launch_bounds__(GS_THREADS) gated_scan_kernel(GatedScanArgs p)
         }
     };
     fetch(t0);
-    const T* vcol = static_cast<const T*>(p.v) + p.v_off + h * p.e + (is_one ? 0 : c);
+    const T* vcol = static_cast<const T*>(p.v) + p.v_off + h * p.e + (live ? c : 0);
     for (int tb = t0; tb < t1; tb += GS_TB) {
         const int nt = min(GS_TB, t1 - tb);
         __syncthreads();
@@ -94,11 +101,18 @@ __global__ void __launch_bounds__(GS_THREADS) gated_scan_kernel(GatedScanArgs p)
         }
         __syncthreads();
         if (tb + GS_TB < t1) fetch(tb + GS_TB);
+        if (ONES && nrm) {
+            const int i = threadIdx.x % DMAX;  // = threadIdx.x; the modulo keeps the shared-memory index in range for the compiler
+            for (int tt = 0; tt < nt; ++tt) {
+                nst = fmaf(as[tt][i], nst, bs[tt][i]);
+                if (MODE != GS_LOCAL) p.nq[(size_t)(tb + tt) * Hd + h * p.d + i0 + i] = nst * qs[tt][i];
+            }
+        }
         if (live) {
-            float vn = is_one ? 1.f : to_f(vcol[(size_t)tb * p.v_pitch]);
+            float vn = to_f(vcol[(size_t)tb * p.v_pitch]);
             for (int tt = 0; tt < nt; ++tt) {
                 const float v = vn;
-                if (!is_one && tt + 1 < nt) vn = to_f(vcol[(size_t)(tb + tt + 1) * p.v_pitch]);
+                if (tt + 1 < nt) vn = to_f(vcol[(size_t)(tb + tt + 1) * p.v_pitch]);
                 float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < DMAX; i += 4) {
@@ -111,18 +125,22 @@ __global__ void __launch_bounds__(GS_THREADS) gated_scan_kernel(GatedScanArgs p)
                     S[i + 3] = fmaf(a4.w, S[i + 3], b4.w * v); o3 = fmaf(S[i + 3], q4.w, o3);
                 }
                 if (MODE != GS_LOCAL) {
-                    float* dst = &p.o[(size_t)(tb + tt) * p.H * ec + h * ec + c];
-                    if (p.key_blocks > 1) atomicAdd(dst, (o0 + o1) + (o2 + o3));
+                    float* dst = &p.o[(size_t)(tb + tt) * p.H * p.e + h * p.e + c];
+                    if (SPLIT) atomicAdd(dst, (o0 + o1) + (o2 + o3));
                     else *dst = (o0 + o1) + (o2 + o3);
                 }
             }
         }
     }
+    // the state goes back through a pointer the compiler cannot see before this point: otherwise it computes the DMAX store addresses
+    // ahead of the token loop and keeps them in registers beside the state (spills at 128 keys)
+    asm volatile("" : "+l"(st));
     if (live && MODE != GS_OUTPUT) {
 #pragma unroll
         for (int i = 0; i < DMAX; ++i)
             if (i0 + i < p.d) st[(size_t)(i0 + i) * ec + c] = S[i];
     }
+    if (ONES && nrm && MODE != GS_OUTPUT) st[(size_t)(i0 + threadIdx.x) * ec + p.e] = nst;
 }
 
 // aprod[(b, h), chunk, i] = product of a_t[h, i] over the chunk's tokens.  grid (B*H, chunks), threads over i
@@ -247,7 +265,9 @@ __global__ void mlstm_qab_kernel(MlstmGateArgs p) {
 
 // ------------------------------------------------------------------------------------------------ after the scan
 struct ScanPostArgs {
-    const float* o;        // [T, H * (e + ones)]
+    const float* o;        // [T, H * e]
+    const float* nq;       // with `ones`: [T, H * d], summed over d to n_t . q_t
+    int d;
     const float* gates;    // [T, H, 3] (exp(-m_t) in entry 2) with `ones`, else null
     const void* w;         // weight: [H*e] (w_per_head) or [e] shared by the heads
     int w_per_head;
@@ -262,11 +282,14 @@ struct ScanPostArgs {
 template <typename T>
 __global__ void __launch_bounds__(128) scan_post_kernel(ScanPostArgs p) {
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    const int ec = p.e + p.ones;
     for (int h = blockIdx.y * nw + warp; h < p.H; h += gridDim.y * nw) {
-        const float* o = p.o + ((size_t)t * p.H + h) * ec;
+        const float* o = p.o + ((size_t)t * p.H + h) * p.e;
         float den = 1.f;
-        if (p.ones) den = fmaxf(fabsf(o[p.e]), p.gates[((size_t)t * p.H + h) * 3 + 2]) + 1e-6f;
+        if (p.ones) {
+            float nq = 0.f;
+            for (int i = lane; i < p.d; i += 32) nq += p.nq[((size_t)t * p.H + h) * p.d + i];
+            den = fmaxf(fabsf(warp_sum(nq)), p.gates[((size_t)t * p.H + h) * 3 + 2]) + 1e-6f;
+        }
         float ss = 0.f;
         for (int c = lane; c < p.e; c += 32) { const float v = o[c] / den; ss = fmaf(v, v, ss); }
         ss = warp_sum(ss);

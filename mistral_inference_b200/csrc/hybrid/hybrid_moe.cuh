@@ -144,6 +144,7 @@ struct MoeSparseArgs {
     int width, ff, E, top;
     int glu;                  // 0: silu(gate) * up, the routing weight multiplies the expert's OUTPUT; 1: the weight multiplies the
     float limit, alpha;       //    expert's INPUT: g = min(w gate, limit), u = clamp(w up, +-limit), act = g sigmoid(alpha g) (u + 1)
+    int accumulate;           // y32 += the experts' sum (y32 is the residual stream) instead of y32 = it
 };
 
 constexpr int MOE_WARPS = 8;
@@ -184,7 +185,10 @@ __global__ void __launch_bounds__(MOE_WARPS * 32) moe_down_sparse_kernel(MoeSpar
         if (e >= a.E) acc += w * to_f(static_cast<const T*>(a.h)[(size_t)t * a.width + n]);
         else acc += w * rnd<T>(warp_dot<T>(wrow + (size_t)e * a.ff, static_cast<const T*>(a.act) + (size_t)slot * a.ff, a.ff, lane));
     }
-    if (lane == 0) a.y32[(size_t)t * a.width + n] = acc;
+    if (lane == 0) {
+        if (a.accumulate) a.y32[(size_t)t * a.width + n] += acc;
+        else a.y32[(size_t)t * a.width + n] = acc;
+    }
 }
 
 // y[t, :] += (sum of dense[t, first .. n - 1]) * h[t, :]

@@ -648,7 +648,7 @@ class MlstmMixer(nn.Module):
     f = logsigmoid(cap tanh(. / cap)); m_t = max(f + m_(t-1), i) (m_0 = 0); S <- exp(f + m_(t-1) - m_t) S + exp(i - m_t) k v^T, n
     likewise with k alone; o = S^T q / (max(|n . q|, exp(-m_t)) + 1e-6); every head divided by its root mean square, times a weight over
     all heads and sigmoid(W_g h).  The state row of a sequence is [heads, dim, vdim + 1] (the normaliser is the last column: a value
-    that is 1 for every token) followed by the heads' m, all fp32.  Packed weights: wqkvg = q ++ k ++ v ++ g rows; wif = i ++ f rows
+    that is 1 for every token; the scan carries it beside the value columns) followed by the heads' m, all fp32.  Packed weights: wqkvg = q ++ k ++ v ++ g rows; wif = i ++ f rows
     (+ bif), whose outputs stay fp32."""
 
     def __init__(self, width: int, a: MlstmArgs, eps: float):
@@ -672,9 +672,9 @@ class MlstmMixer(nn.Module):
         qkvg = _h.linear(hn, self.wqkvg)
         gif = _h.linear(hn, self.wif, self.bif, epi=_h.EPI_F32)
         gates, qab = _h.mlstm_gates(qkvg, gif, view.state, self.m_off, md.q_start, md.seqpos, md.slots, B, a.heads, a.dim, a.gate_cap, a.dim ** -0.5)
-        o32 = _h.gated_scan(qab, qkvg, qkvg.shape[1], 2 * self.nqk, view.state, md.q_start, md.seqpos, md.slots, B, a.heads, a.dim, a.vdim, ones=True,
-                            max_seqlen=md.max_seqlen)
-        y = _h.scan_post(o32, gates, self.norm, True, qkvg, qkvg.shape[1], 2 * self.nqk + self.nv, a.heads, a.vdim, True, self.eps)
+        o32, nq = _h.gated_scan(qab, qkvg, qkvg.shape[1], 2 * self.nqk, view.state, md.q_start, md.seqpos, md.slots, B, a.heads, a.dim, a.vdim,
+                                ones=True, max_seqlen=md.max_seqlen)
+        y = _h.scan_post(o32, gates, self.norm, True, qkvg, qkvg.shape[1], 2 * self.nqk + self.nv, a.heads, a.vdim, True, self.eps, nq=nq)
         project_out(y, self.wo, x32, post, scale)
 
     def checkpoint_names(self) -> List[str]:
@@ -720,7 +720,7 @@ class ScaledInputMoe(nn.Module):
         a = self.a
         dense, idx, wsel = _h.moe_route(hn, self.router, None, 1, 1, a.top, score=1)
         if hn.shape[0] <= self.sparse_max_tokens:
-            x32.add_(_h.moe_sparse(hn, self.w13, self.w2, idx, wsel, a.experts, a.ff, glu=True, limit=a.limit, alpha=a.alpha))
+            _h.moe_sparse(hn, self.w13, self.w2, idx, wsel, a.experts, a.ff, glu=True, limit=a.limit, alpha=a.alpha, add_to=x32)
         else:
             act = _h.linear_glu(hn, self.w13, a.limit, a.alpha, rowscale=dense, group=a.ff)
             _h.linear(act, self.w2, epi=_h.EPI_RESIDUAL, residual=x32)
