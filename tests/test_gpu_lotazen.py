@@ -29,6 +29,11 @@ SHAPES = {
         (mlstm_cfg(2, 72, 136, 10.0), moe_cfg(ff=32, experts=6, top=2, shared=(16, 2.0))),
         (side_cfg(left=attn_cfg(4, 2, 32, 32, 0.35, 70, (10000.0, 16, 2.0)), right={"heads": 2, "dim": 16, "vdim": 16}), moe_cfg(ff=32, experts=4, top=1)),
         (side_cfg(left=attn_cfg(2, 1, 64, 64, 0.2, 33, (500.0, 64, 4.0)), right={"heads": 1, "dim": 64, "vdim": 130}), None)]),
+    # nothing is a multiple of 2, 4 or 8 where it need not be: width 30, odd head sizes (the last entry of a head has no partner to
+    # rotate with), 3 query heads on 1 key/value head, 17 words
+    "awkward": dict(width=30, vocab=17, layers=[
+        (side_cfg(left=attn_cfg(3, 1, 7, 5, 0.5, 9, (10000.0, 6, 1.5)), right={"heads": 2, "dim": 5, "vdim": 9}), moe_cfg(ff=7, experts=3, top=2, shared=(5, 1.0))),
+        (mlstm_cfg(2, 7, 3, 4.0), moe_cfg(ff=6, experts=2, top=1, shared=None))]),
     # everything 1: one head, one expert of which one is used, a window that shows only the token itself, rotation of one pair
     "one": dict(width=24, vocab=20, softcap=3.0, layers=[
         (side_cfg(left=attn_cfg(1, 1, 8, 8, 1.0, 1, (10.0, 2, 1.0)), right={"heads": 1, "dim": 4, "vdim": 4}, left_scale=1.0, right_scale=1.0),
