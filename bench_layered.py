@@ -439,7 +439,15 @@ def lotazen_kernel_table(s: dict, T: int, ctx: int, peaks: dict, dev) -> dict:
     q2, o2 = q[:B].contiguous(), torch.empty(B, H * d, device=dev, dtype=bf)
     rec(f"attn_window decode B={B} (ring of {md2.window})",
         _time(lambda: h.attn_window(q2, ring.cache_k[0], ring.cache_v[0], md2.positions, md2.q_start, md2.slots, o2, B, md2.window, H, G, d, d, 0.09, win,
-                                    splits=h.attn_splits(B, H, md2.window)), 3, 8, flush), bytes_=2.0 * B * min(ctx + 1, win) * G * d * 2)
+                                    splits=h.window_decode_plan(B, H, md2.window)[0], chunk=h.window_decode_plan(B, H, md2.window)[1]), 3, 8, flush),
+        bytes_=2.0 * B * min(ctx + 1, win) * G * d * 2)
+    q1, o1 = q[:1].contiguous(), torch.empty(1, H * d, device=dev, dtype=bf)
+    ring.reset(); ring.init_kvseqlens(1); ring.update_seqlens([ctx])
+    md1 = ring.get_input_metadata([1])[0]
+    for label, (sp, ch) in (("128-key chunks", (h.attn_splits(1, H, md1.window), 0)), ("planned chunks", h.window_decode_plan(1, H, md1.window))):
+        rec(f"attn_window decode B=1 (ring of {md1.window}), {label}: {sp} splits",
+            _time(lambda: h.attn_window(q1, ring.cache_k[0], ring.cache_v[0], md1.positions, md1.q_start, md1.slots, o1, 1, md1.window, H, G, d, d, 0.09, win,
+                                        splits=sp, chunk=ch), 3, 8, flush), bytes_=2.0 * min(ctx + 1, win) * G * d * 2)
     rec(f"like: attn_bias decode B={B} ctx={ctx}",
         _time(lambda: h.attn_bias(q2, full.cache_k[0], full.cache_v[0], tab, md2f.positions, md2f.q_start, md2f.slots, o2, B, ctx + 8, H, G, d, d, 0.09,
                                   splits=h.attn_splits(B, H, ctx + 8)), 3, 8, flush), bytes_=2.0 * B * (ctx + 1) * G * d * 2)

@@ -138,11 +138,13 @@ int mbh_rows_axpy(void* y32, const void* h, const void* dense, int64_t T, int64_
 /* mbh_attn_bias with a sliding window and a ring that may be shorter than the sequence.  window > 0: the token at position p sees keys
  * p - window + 1 .. p only.  own_k [T, G*d] / own_v [T, G*e] (token-major, with seqpos [B] = tokens cached before this call): keys and
  * values of THIS call's tokens, read from there instead of the ring, so that a prompt longer than the ring finds all its keys; the ring
- * is written after attention (mbh_kv_scatter).  Without them every visible key must be in the ring (W >= min(window, sequence length)). */
+ * is written after attention (mbh_kv_scatter).  Without them every visible key must be in the ring (W >= min(window, sequence length)).
+ * chunk: keys per warp and step of the exact kernel, 1 .. 128 (0: 128); with `splits` CTAs of 4 warps per (token, head) a CTA takes
+ * 4 * chunk keys per round, so a short ring read by few tokens is spread over splits = ceil(W / (4 * chunk)) CTAs. */
 int mbh_attn_window(const void* q, const void* cache_k, const void* cache_v, const void* bias_tab, int64_t n_tab, const void* positions,
                     const void* q_start, const void* slots, void* out, int64_t T, int64_t B, int64_t W, int64_t H, int64_t G, int64_t d, int64_t e,
                     float scale, int64_t n_tiles, int64_t splits, void* scratch, int64_t window, const void* own_k, const void* own_v,
-                    const void* seqpos, int dt, void* stream);
+                    const void* seqpos, int64_t chunk, int dt, void* stream);
 
 /* Linear with interleaved gate/up rows and the clamped gated unit of mbh_linear's epilogue 2; gate and up of column c are multiplied by
  * rowscale[m, c / rs_group] (fp32 [M, rs_pitch]; null: 1) BEFORE the clamps.  mbh_glu_epilogue applies the same to y[M, N] of another GEMM. */

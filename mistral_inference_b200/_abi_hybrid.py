@@ -43,7 +43,7 @@ _SIGNATURES = {
     "mbh_latent_vup": (c_int, [P, P, P, I, I, P, I, I, I, I, c_int, P]),
     "mbh_moe_route": (c_int, [P, P, P, P, P, P, I, I, I, I, I, I, c_int, c_int, P]),
     "mbh_moe_sparse": (c_int, [P, P, P, P, P, P, P, I, I, I, I, I, c_int, F, F, c_int, c_int, P]),
-    "mbh_attn_window": (c_int, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, I, P, P, P, c_int, P]),
+    "mbh_attn_window": (c_int, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, I, P, P, P, I, c_int, P]),
     "mbh_linear_glu": (c_int, [P, P, P, I, I, I, F, F, P, I, I, c_int, P]),
     "mbh_glu_epilogue": (c_int, [P, P, I, I, F, F, P, I, I, c_int, P]),
     "mbh_embed_pos": (c_int, [P, P, P, P, F, P, I, I, c_int, P]),
@@ -374,12 +374,22 @@ def kv_scatter(k, v, cache_rows, ring_k, ring_v) -> None:
 
 
 def attn_window(q, cache_k, cache_v, positions, q_start, slots, out, B: int, W: int, H: int, G: int, d: int, e: int, scale: float, window: int,
-                own_k=None, own_v=None, seqpos=None, n_tiles: int = 0, splits: int = 1) -> None:
-    """`attn_bias` without a bias, with a sliding window (0: none) and, for prompts, this call's own keys and values beside the ring."""
+                own_k=None, own_v=None, seqpos=None, n_tiles: int = 0, splits: int = 1, chunk: int = 0) -> None:
+    """`attn_bias` without a bias, with a sliding window (0: none) and, for prompts, this call's own keys and values beside the ring.
+    chunk: keys per warp and step of the exact kernel (0: 128), see `window_decode_plan`."""
     scratch = torch.empty(q.shape[0] * H * splits * (2 + e), dtype=torch.float32, device=q.device) if splits > 1 and n_tiles == 0 else None
     _check(lib().mbh_attn_window(_ptr(q), _ptr(cache_k), _ptr(cache_v), None, 0, _ptr(positions), _ptr(q_start), _ptr(slots), _ptr(out), q.shape[0], B, W,
-                                 H, G, d, e, scale, n_tiles, splits, _ptr(scratch), window, _ptr(own_k), _ptr(own_v), _ptr(seqpos), dt_of(q.dtype),
-                                 _stream()), "mbh_attn_window")
+                                 H, G, d, e, scale, n_tiles, splits, _ptr(scratch), window, _ptr(own_k), _ptr(own_v), _ptr(seqpos), chunk,
+                                 dt_of(q.dtype), _stream()), "mbh_attn_window")
+
+
+def window_decode_plan(T: int, H: int, W: int, n_sm: int = 148):
+    """(splits, chunk) of a decode step over a ring of W rows: a CTA of 4 warps takes 4 * chunk keys per round.  Few (token, head)
+    pairs over a short ring (a small batch, a sliding window) get 32-key chunks and one round per CTA, so that the ring is spread
+    over up to 4 CTAs per SM; larger batches keep 128-key chunks.  A function of the batch and the ring only (CUDA-graph decode)."""
+    chunk = 32 if T * H * ((W + 511) // 512) < n_sm else 128
+    splits = max(1, min((W + 4 * chunk - 1) // (4 * chunk), (4 * n_sm) // max(T * H, 1), 64))
+    return int(splits), chunk
 
 
 # ------------------------------------------------------------------------------------------------ gated linear recurrences

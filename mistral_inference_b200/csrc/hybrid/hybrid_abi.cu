@@ -198,21 +198,22 @@ int mbh_attn_bias(const void* q, const void* cache_k, const void* cache_v, const
                   const void* q_start, const void* slots, void* out, int64_t T, int64_t B, int64_t W, int64_t H, int64_t G, int64_t d, int64_t e,
                   float scale, int64_t n_tiles, int64_t splits, void* scratch, int dt, void* stream) {
     return mbh_attn_window(q, cache_k, cache_v, bias_tab, n_tab, positions, q_start, slots, out, T, B, W, H, G, d, e, scale, n_tiles, splits, scratch,
-                           0, nullptr, nullptr, nullptr, dt, stream);
+                           0, nullptr, nullptr, nullptr, 0, dt, stream);
 }
 
 int mbh_attn_window(const void* q, const void* cache_k, const void* cache_v, const void* bias_tab, int64_t n_tab, const void* positions,
                     const void* q_start, const void* slots, void* out, int64_t T, int64_t B, int64_t W, int64_t H, int64_t G, int64_t d, int64_t e,
                     float scale, int64_t n_tiles, int64_t splits, void* scratch, int64_t window, const void* own_k, const void* own_v,
-                    const void* seqpos, int dt, void* stream) {
+                    const void* seqpos, int64_t chunk, int dt, void* stream) {
     if (T == 0) return 0;
+    if (chunk < 0 || chunk > AT_CHUNK) return bad("mbh_attn_window: chunk is 0 (default) or 1 .. 128 keys");
     if (e > 32 * AT_MAXR) return bad("mbh_attn_bias: value size above 256");
     if (H % G) return bad("mbh_attn_bias: heads must be a multiple of kv heads");
     if (splits > AT_MAX_SPLITS) return bad("mbh_attn_bias: at most 64 splits");
     if (window < 0 || (!own_k != !own_v) || (own_k && !seqpos)) return bad("mbh_attn_window: window >= 0; own keys, own values and seqpos come together");
     AttnArgs a{q, cache_k, cache_v, (const float*)bias_tab, (int)n_tab, (const int*)positions, (const int*)q_start, (const int*)slots, out,
                (int)T, (int)B, (int)W, (int)H, (int)G, (int)d, (int)e, scale, (int)(splits > 1 && scratch ? splits : 1), (float*)scratch, 0, 0,
-               (int)window, own_k, own_v, (const int*)seqpos};
+               (int)window, own_k, own_v, (const int*)seqpos, (int)chunk};
     const size_t smem = sizeof(float) * ((size_t)d + AT_WARPS * AT_CHUNK + AT_WARPS * (2 + 32 * AT_MAXR));
     cudaStream_t st = (cudaStream_t)stream;
     // prompts in bf16: the tensor-core kernel, when the caller counted the 64-query tiles and the sizes are instantiated

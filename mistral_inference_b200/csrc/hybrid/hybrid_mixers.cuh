@@ -132,6 +132,8 @@ struct AttnArgs {
                             // [T, G*d] / [T, G*e]; key j >= seqpos[b] is row q_start[b] + j - seqpos[b] there, older keys are in the ring
                             // (which this call's tokens are written to only after attention).  null: every key is in the ring.
     const int* seqpos;      // [B] tokens cached before this call (with own_k)
+    int chunk;              // keys per warp and step, at most AT_CHUNK (0: AT_CHUNK).  A short ring read by few (token, head) pairs -- a decode
+                            // step of a small batch over a sliding window -- is spread over more CTAs with a smaller chunk
 };
 
 // where key / value j of a sequence lives: this call's own rows, or the ring
@@ -178,8 +180,9 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
 #pragma unroll
     for (int r = 0; r < MAXR; ++r) acc[r] = 0.f;
     const int cpl = (a.e + 31) / 32;  // value columns per lane: lane * cpl .. + cpl - 1
-    for (int c0 = lo + (blockIdx.y * AT_WARPS + warp) * AT_CHUNK; c0 < n; c0 += a.splits * AT_WARPS * AT_CHUNK) {
-        const int cn = min(AT_CHUNK, n - c0);
+    const int CH = a.chunk > 0 ? a.chunk : AT_CHUNK;
+    for (int c0 = lo + (blockIdx.y * AT_WARPS + warp) * CH; c0 < n; c0 += a.splits * AT_WARPS * CH) {
+        const int cn = min(CH, n - c0);
         float cmax = -INFINITY;
         for (int jj = lane; jj < cn; jj += 32) {
             const int j = c0 + jj;

@@ -541,8 +541,9 @@ class RotaryWindowAttention(nn.Module):
         else:
             q, _, _ = _h.rot_prep(qkv, self.frequencies(), md.positions, md.cache_rows, view.cache_k, view.cache_v, a.heads, a.kv_heads, a.dim, a.vdim,
                                   a.rot_dims, a.unit_norm, self.eps, own=False)
+            splits, chunk = _h.window_decode_plan(T, a.heads, W)
             _h.attn_window(q, view.cache_k, view.cache_v, md.positions, md.q_start, md.slots, out, B, W, a.heads, a.kv_heads, a.dim, a.vdim, a.scale,
-                           window, splits=_h.attn_splits(T, a.heads, W))
+                           window, splits=splits, chunk=chunk)
         project_out(out, self.wo, x32, post, scale)
 
     def checkpoint_names(self) -> List[str]:
