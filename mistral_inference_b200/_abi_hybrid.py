@@ -383,12 +383,13 @@ def attn_window(q, cache_k, cache_v, positions, q_start, slots, out, B: int, W: 
                                  dt_of(q.dtype), _stream()), "mbh_attn_window")
 
 
-def window_decode_plan(T: int, H: int, W: int, n_sm: int = 148):
-    """(splits, chunk) of a decode step over a ring of W rows: a CTA of 4 warps takes 4 * chunk keys per round.  Few (token, head)
-    pairs over a short ring (a small batch, a sliding window) get 32-key chunks and one round per CTA, so that the ring is spread
-    over up to 4 CTAs per SM; larger batches keep 128-key chunks.  A function of the batch and the ring only (CUDA-graph decode)."""
-    chunk = 32 if T * H * ((W + 511) // 512) < n_sm else 128
-    splits = max(1, min((W + 4 * chunk - 1) // (4 * chunk), (4 * n_sm) // max(T * H, 1), 64))
+def window_decode_plan(T: int, H: int, W: int):
+    """(splits, chunk) of a decode step over a ring of W rows: a CTA of 4 warps takes 4 * chunk keys per round.  32-key chunks (a
+    key per lane) and one round per CTA measured fastest from 1 to 32 sequences over rings of 72 to 4096 rows: a decode step's
+    attention is latency, not bandwidth, and the ring is spread over ceil(W / 128) CTAs per (token, head) -- fewer when the batch
+    alone gives thousands of CTAs.  A function of the batch and the ring only (CUDA-graph decode)."""
+    chunk = 32
+    splits = max(1, min((W + 4 * chunk - 1) // (4 * chunk), 8192 // max(T * H, 1), 64))
     return int(splits), chunk
 
 
