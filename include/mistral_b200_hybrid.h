@@ -13,7 +13,7 @@
 extern "C" {
 #endif
 
-#define MBH_ABI_VERSION 3
+#define MBH_ABI_VERSION 4
 
 int mbh_abi_version(void);
 const char* mbh_last_error(void);
@@ -120,14 +120,15 @@ int mbh_latent_vup(const void* o_lat, const void* w_uv, const void* gate, int64_
 
 /* Router of a mixture of experts, fp32: s = softmax(W_r h) over n outputs (score 0) or sigmoid of each output (score 1), choice = s + correction (null: none); the outputs form
  * `groups` equal groups of neighbours and only those of the `keep` groups with the largest choice stay eligible; the `top` largest
- * eligible choices are taken, weighted by s.  dense: fp32 [T, n] (0 where not chosen); idx int32 / wsel fp32 [T, top]. */
+ * eligible choices are taken, weighted by s * scale.  dense: fp32 [T, n] (0 where not chosen); idx int32 / wsel fp32 [T, top]. */
 int mbh_moe_route(const void* h, const void* w_router, const void* correction, void* dense, void* idx, void* wsel, int64_t T, int64_t width,
-                  int64_t n, int64_t groups, int64_t keep, int64_t top, int score, int dt, void* stream);
+                  int64_t n, int64_t groups, int64_t keep, int64_t top, int score, float scale, int dt, void* stream);
 
 /* The chosen experts of few tokens: y32 [T, width] = sum_k wsel[t, k] * expert(idx[t, k])(h[t]); an index >= E is an identity
  * expert (output = h[t]).  w13 [E * 2 * ff, width] (gate and up rows interleaved), w2 [width, E * ff]; act: scratch [T * top, ff].
  * glu 0: experts silu(gate) * up.  glu 1: the weight multiplies the expert's INPUT and the unit is the clamped one of mbh_linear's
  * epilogue 2: y32 = sum_k expert(wsel[t, k] * h[t]), g = min(w gate, limit), u = clamp(w up, -limit, limit).
+ * glu 2: experts without a gate, W_down max(W_up h, 0)^2, with w13 [E * ff, width] plain rows; the weight multiplies the OUTPUT.
  * accumulate 1: the sum is ADDED to y32 (the fp32 residual stream) instead of stored. */
 int mbh_moe_sparse(const void* h, const void* w13, const void* w2, const void* idx, const void* wsel, void* act, void* y32, int64_t T, int64_t width,
                    int64_t ff, int64_t E, int64_t top, int glu, float limit, float alpha, int accumulate, int dt, void* stream);
@@ -140,11 +141,13 @@ int mbh_rows_axpy(void* y32, const void* h, const void* dense, int64_t T, int64_
  * values of THIS call's tokens, read from there instead of the ring, so that a prompt longer than the ring finds all its keys; the ring
  * is written after attention (mbh_kv_scatter).  Without them every visible key must be in the ring (W >= min(window, sequence length)).
  * chunk: keys per warp and step of the exact kernel, 1 .. 128 (0: 128); with `splits` CTAs of 4 warps per (token, head) a CTA takes
- * 4 * chunk keys per round, so a short ring read by few tokens is spread over splits = ceil(W / (4 * chunk)) CTAs. */
+ * 4 * chunk keys per round, so a short ring read by few tokens is spread over splits = ceil(W / (4 * chunk)) CTAs.
+ * weights 0: softmax over the visible keys.  weights 1: every visible key weighs sigmoid(score) and nothing is normalised (bias_tab with
+ * n_tab = 1 is then a number per head inside the sigmoid). */
 int mbh_attn_window(const void* q, const void* cache_k, const void* cache_v, const void* bias_tab, int64_t n_tab, const void* positions,
                     const void* q_start, const void* slots, void* out, int64_t T, int64_t B, int64_t W, int64_t H, int64_t G, int64_t d, int64_t e,
                     float scale, int64_t n_tiles, int64_t splits, void* scratch, int64_t window, const void* own_k, const void* own_v,
-                    const void* seqpos, int64_t chunk, int dt, void* stream);
+                    const void* seqpos, int64_t chunk, int weights, int dt, void* stream);
 
 /* Linear with interleaved gate/up rows and the clamped gated unit of mbh_linear's epilogue 2; gate and up of column c are multiplied by
  * rowscale[m, c / rs_group] (fp32 [M, rs_pitch]; null: 1) BEFORE the clamps.  mbh_glu_epilogue applies the same to y[M, N] of another GEMM. */
@@ -191,9 +194,46 @@ int mbh_mlstm_gates(const void* qkvg, const void* gif, void* gates, void* qab, v
                     void* stream);
 
 /* After a scan: o = o32[t, h, :e] (divided by max(|sum_i nq[t, h, i]|, gates[t, h, 2]) + 1e-6 with ones = 1; nq [T, H * d]); y = o / sqrt(mean(o^2) + eps) * w
- * (w [H*e] with w_per_head, else [e] shared by the heads) * sigmoid(gate[t * g_pitch + g_off + h*e + c]) (gate null: none).  y [T, H*e]. */
+ * (w [H*e] with w_per_head, else [e] shared by the heads; null: no weight) * act(gate[t * g_pitch + g_off + h*e + c]) (gate null: none;
+ * gate_act 0: sigmoid, 1: SiLU).  y [T, H*e]. */
 int mbh_scan_post(const void* o32, const void* nq, int64_t d, const void* gates, const void* w, int w_per_head, const void* gate, int64_t g_pitch,
-                  int64_t g_off, void* y, int64_t T, int64_t H, int64_t e, int ones, float eps, int dt, void* stream);
+                  int64_t g_off, int gate_act, void* y, int64_t T, int64_t H, int64_t e, int ones, float eps, int dt, void* stream);
+
+/* h[t] = x32[t] + sum_j w[:, j] * x32[t - taps + 1 + j] over the tokens of t's sequence: a causal convolution over time on every channel
+ * (w [D, taps], storage type), added to its input; inputs before the sequence's start are zero.  The last taps - 1 inputs of the
+ * sequence in slot s are kept, fp32 [taps - 1, D], at state + s * state_stride + state_off: read when seqpos[b] > 0, written back by
+ * this call.  h [T, D] storage type.  one_each = 1: one token per sequence (T == B), one launch. */
+int mbh_canon_conv(const void* x32, const void* w, void* state, int64_t state_stride, int64_t state_off, const void* q_start, const void* seqpos,
+                   const void* slots, void* h, int64_t T, int64_t B, int64_t D, int64_t taps, int one_each, int dt, void* stream);
+
+/* acc32[t] += y32[t] / sqrt(mean(y32[t]^2) + eps) * w (fp32 rows [T, D]; w storage type): the norm of a sublayer's output on its way into
+ * the residual stream.  With stack: afterwards out32[t] = sum_(j < n - 1) coef[j] * stack[j * stack_stride + t * D ..] + coef[n - 1] *
+ * acc32[t], the weighted average over the results of the layers so far (coef [n] storage type; stack_stride in floats). */
+int mbh_rmsnorm_add(const void* y32, const void* w, void* acc32, int64_t T, int64_t D, float eps, const void* stack, int64_t stack_stride,
+                    const void* coef, int64_t n, void* out32, int dt, void* stream);
+
+/* out32[i] = sum_(j < n) coef[j] * stack[j * stack_stride + i], i < count. */
+int mbh_depth_mix(const void* stack, int64_t stack_stride, const void* coef, int64_t n, void* out32, int64_t count, int dt, void* stream);
+
+/* Retention gates from qk [T, pitch] = q (H*d) | k (H*d) | ...: the first rot_dims entries of each head turn by positions[t] * freq[i]
+ * (freq float64 [rot_dims / 2]), entry i paired with entry i + rot_dims / 2; qab fp32 [T, 3, H*d] = rot(q) | decay[h] | rot(k) * kscale. */
+int mbh_retention_qab(const void* qk, int64_t pitch, const void* freq, const void* decay, const void* positions, void* qab, int64_t T, int64_t H,
+                      int64_t d, int64_t rot_dims, float kscale, int dt, void* stream);
+
+/* Gated-linear-attention gates: qab fp32 [T, 3, Hd] = q * qscale | exp(logsigmoid(z32) * inv_tau) | k, z32 fp32 [T, Hd]. */
+int mbh_gla_qab(const void* qk, int64_t pitch, const void* z32, void* qab, int64_t T, int64_t Hd, float qscale, float inv_tau, int dt, void* stream);
+
+/* Splits qkv [T, Nq + Nk + Nv]; q <- rms_norm(q) * qnorm over all Nq entries, k <- rms_norm(k) * knorm over all Nk entries.  Outputs as
+ * mbh_rot_prep: q_out [T, Nq]; k_out / v_out token-major or null; ring rows cache_rows[t] (null: no ring write; -1: not cached). */
+int mbh_whole_norm_prep(const void* qkv, const void* qnorm, const void* knorm, const void* cache_rows, void* q_out, void* k_out, void* v_out,
+                        void* ring_k, void* ring_v, int64_t T, int64_t Nq, int64_t Nk, int64_t Nv, float eps, int dt, void* stream);
+
+/* out[M, N] = max(x W^T, 0)^2 * rowscale[m, n / rs_group] (rowscale fp32 [M, rs_pitch] or null); mbh_relu2_epilogue applies the same to
+ * y[M, N] (N even) of another GEMM. */
+int mbh_linear_relu2(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, const void* rowscale, int64_t rs_pitch,
+                     int64_t rs_group, int dt, void* stream);
+int mbh_relu2_epilogue(const void* y, void* out, int64_t M, int64_t N, const void* rowscale, int64_t rs_pitch, int64_t rs_group, int dt,
+                       void* stream);
 
 #ifdef __cplusplus
 }

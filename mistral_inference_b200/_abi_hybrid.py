@@ -13,7 +13,7 @@ import torch
 from . import _abi, build
 from ._abi import Mb200Error
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 EPI_STORE, EPI_RESIDUAL, EPI_GLU, EPI_F32, EPI_RESIDUAL_SCALED = 0, 1, 2, 3, 5
 _DT = {torch.bfloat16: 0, torch.float32: 1}
 _lib: Optional[ctypes.CDLL] = None
@@ -41,9 +41,9 @@ _SIGNATURES = {
     "mbh_attn_latent": (c_int, [P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, c_int, P]),
     "mbh_attn_latent_decode": (c_int, [P, P, P, P, P, I, I, I, I, I, F, I, P, c_int, P]),
     "mbh_latent_vup": (c_int, [P, P, P, I, I, P, I, I, I, I, c_int, P]),
-    "mbh_moe_route": (c_int, [P, P, P, P, P, P, I, I, I, I, I, I, c_int, c_int, P]),
+    "mbh_moe_route": (c_int, [P, P, P, P, P, P, I, I, I, I, I, I, c_int, F, c_int, P]),
     "mbh_moe_sparse": (c_int, [P, P, P, P, P, P, P, I, I, I, I, I, c_int, F, F, c_int, c_int, P]),
-    "mbh_attn_window": (c_int, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, I, P, P, P, I, c_int, P]),
+    "mbh_attn_window": (c_int, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, I, P, P, P, I, c_int, c_int, P]),
     "mbh_linear_glu": (c_int, [P, P, P, I, I, I, F, F, P, I, I, c_int, P]),
     "mbh_glu_epilogue": (c_int, [P, P, I, I, F, F, P, I, I, c_int, P]),
     "mbh_embed_pos": (c_int, [P, P, P, P, F, P, I, I, c_int, P]),
@@ -52,7 +52,15 @@ _SIGNATURES = {
     "mbh_gated_scan": (c_int, [P, P, I, I, P, I, P, P, P, P, P, I, I, I, I, I, c_int, I, I, P, c_int, P]),
     "mbh_hgrn2_gates": (c_int, [P, P, P, I, I, I, c_int, P]),
     "mbh_mlstm_gates": (c_int, [P, P, P, P, P, I, I, P, P, P, I, I, I, I, I, F, F, c_int, P]),
-    "mbh_scan_post": (c_int, [P, P, I, P, P, c_int, P, I, I, P, I, I, I, c_int, F, c_int, P]),
+    "mbh_scan_post": (c_int, [P, P, I, P, P, c_int, P, I, I, c_int, P, I, I, I, c_int, F, c_int, P]),
+    "mbh_canon_conv": (c_int, [P, P, P, I, I, P, P, P, P, I, I, I, I, c_int, c_int, P]),
+    "mbh_rmsnorm_add": (c_int, [P, P, P, I, I, F, P, I, P, I, P, c_int, P]),
+    "mbh_depth_mix": (c_int, [P, I, P, I, P, I, c_int, P]),
+    "mbh_retention_qab": (c_int, [P, I, P, P, P, P, I, I, I, I, F, c_int, P]),
+    "mbh_gla_qab": (c_int, [P, I, P, P, I, I, F, F, c_int, P]),
+    "mbh_whole_norm_prep": (c_int, [P, P, P, P, P, P, P, P, P, I, I, I, I, F, c_int, P]),
+    "mbh_linear_relu2": (c_int, [P, P, P, I, I, I, P, I, I, c_int, P]),
+    "mbh_relu2_epilogue": (c_int, [P, P, I, I, P, I, I, c_int, P]),
     "mbh_rows_axpy": (c_int, [P, P, P, I, I, I, I, c_int, P]),
 }
 
@@ -232,22 +240,25 @@ def linear_swiglu(x: torch.Tensor, w: torch.Tensor, rowscale: Optional[torch.Ten
     return out
 
 
-def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], groups: int, keep: int, top: int, score: int = 0):
-    """(dense fp32 [T, n], idx int32 [T, top], wsel fp32 [T, top]) of the fp32 router; score 0: softmax, 1: sigmoid."""
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], groups: int, keep: int, top: int, score: int = 0,
+              scale: float = 1.0):
+    """(dense fp32 [T, n], idx int32 [T, top], wsel fp32 [T, top]) of the fp32 router; score 0: softmax, 1: sigmoid; the weights are the
+    chosen scores times `scale`."""
     T, D = h.shape
     n = w_router.shape[0]
     dense = torch.empty(T, n, dtype=torch.float32, device=h.device)
     idx = torch.empty(T, top, dtype=torch.int32, device=h.device)
     wsel = torch.empty(T, top, dtype=torch.float32, device=h.device)
     _check(lib().mbh_moe_route(_ptr(h), _ptr(w_router), _ptr(correction), _ptr(dense), _ptr(idx), _ptr(wsel), T, D, n, groups, keep, top, score,
-                               dt_of(h.dtype), _stream()), "mbh_moe_route")
+                               scale, dt_of(h.dtype), _stream()), "mbh_moe_route")
     return dense, idx, wsel
 
 
 def moe_sparse(h: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, idx: torch.Tensor, wsel: torch.Tensor, E: int, ff: int,
-               glu: bool = False, limit: float = 0.0, alpha: float = 0.0, add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
+               glu: int = 0, limit: float = 0.0, alpha: float = 0.0, add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
     """fp32 [T, width]: the weighted sum of each token's chosen experts (indices >= E: identity), streaming only their weights.
-    glu: clamped gated experts whose INPUT is multiplied by the routing weight.  add_to (fp32 [T, width], the residual stream): the
+    glu 1 (True): clamped gated experts whose INPUT is multiplied by the routing weight; glu 2: experts without a gate,
+    W_down max(W_up h, 0)^2, with w13 [E * ff, width] plain rows.  add_to (fp32 [T, width], the residual stream): the
     sum is added to it in place instead of returned in a new tensor."""
     T, D = h.shape
     top = idx.shape[1]
@@ -374,13 +385,15 @@ def kv_scatter(k, v, cache_rows, ring_k, ring_v) -> None:
 
 
 def attn_window(q, cache_k, cache_v, positions, q_start, slots, out, B: int, W: int, H: int, G: int, d: int, e: int, scale: float, window: int,
-                own_k=None, own_v=None, seqpos=None, n_tiles: int = 0, splits: int = 1, chunk: int = 0) -> None:
+                own_k=None, own_v=None, seqpos=None, n_tiles: int = 0, splits: int = 1, chunk: int = 0, head_bias=None) -> None:
     """`attn_bias` without a bias, with a sliding window (0: none) and, for prompts, this call's own keys and values beside the ring.
-    chunk: keys per warp and step of the exact kernel (0: 128), see `window_decode_plan`."""
+    chunk: keys per warp and step of the exact kernel (0: 128), see `window_decode_plan`.  head_bias (fp32 [H]): sigmoid weights instead
+    of the softmax, every visible key weighing sigmoid(score + head_bias[h]), not normalised."""
     scratch = torch.empty(q.shape[0] * H * splits * (2 + e), dtype=torch.float32, device=q.device) if splits > 1 and n_tiles == 0 else None
-    _check(lib().mbh_attn_window(_ptr(q), _ptr(cache_k), _ptr(cache_v), None, 0, _ptr(positions), _ptr(q_start), _ptr(slots), _ptr(out), q.shape[0], B, W,
-                                 H, G, d, e, scale, n_tiles, splits, _ptr(scratch), window, _ptr(own_k), _ptr(own_v), _ptr(seqpos), chunk,
-                                 dt_of(q.dtype), _stream()), "mbh_attn_window")
+    assert head_bias is None or (head_bias.dtype == torch.float32 and head_bias.numel() == H)
+    _check(lib().mbh_attn_window(_ptr(q), _ptr(cache_k), _ptr(cache_v), _ptr(head_bias), int(head_bias is not None), _ptr(positions), _ptr(q_start),
+                                 _ptr(slots), _ptr(out), q.shape[0], B, W, H, G, d, e, scale, n_tiles, splits, _ptr(scratch), window, _ptr(own_k),
+                                 _ptr(own_v), _ptr(seqpos), chunk, int(head_bias is not None), dt_of(q.dtype), _stream()), "mbh_attn_window")
 
 
 def window_decode_plan(T: int, H: int, W: int):
@@ -434,11 +447,15 @@ def mlstm_gates(qkvg, gif, state, m_off: int, q_start, seqpos, slots, B: int, H:
     return gates, qab
 
 
-def scan_post(o32, gates, w, w_per_head: bool, gate, g_pitch: int, g_off: int, H: int, e: int, ones: bool, eps: float, nq=None) -> torch.Tensor:
+def scan_post(o32, gates, w, w_per_head: bool, gate, g_pitch: int, g_off: int, H: int, e: int, ones: bool, eps: float, nq=None, silu_gate: bool = False,
+              dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Every head of o32 divided by its root mean square, times w (None: no weight; then `dtype` names the storage type) and the gate's
+    sigmoid (silu_gate: its SiLU)."""
     T = o32.shape[0]
-    y = torch.empty(T, H * e, dtype=w.dtype, device=o32.device)
-    _check(lib().mbh_scan_post(_ptr(o32), _ptr(nq), nq.shape[1] // H if nq is not None else 0, _ptr(gates), _ptr(w), int(w_per_head), _ptr(gate), g_pitch, g_off, _ptr(y), T, H, e, int(ones), eps,
-                               dt_of(w.dtype), _stream()), "mbh_scan_post")
+    dtype = w.dtype if w is not None else (gate.dtype if gate is not None else dtype)
+    y = torch.empty(T, H * e, dtype=dtype, device=o32.device)
+    _check(lib().mbh_scan_post(_ptr(o32), _ptr(nq), nq.shape[1] // H if nq is not None else 0, _ptr(gates), _ptr(w), int(w_per_head), _ptr(gate), g_pitch, g_off,
+                               int(silu_gate), _ptr(y), T, H, e, int(ones), eps, dt_of(dtype), _stream()), "mbh_scan_post")
     return y
 
 
@@ -459,4 +476,84 @@ def linear_glu(x: torch.Tensor, w: torch.Tensor, limit: float, alpha: float, row
         _check(lib().mbh_glu_epilogue(_ptr(y), _ptr(out), M, N, limit, alpha, _ptr(rowscale), pitch, group, dt_of(x.dtype), _stream()), "mbh_glu_epilogue")
         return out
     _check(lib().mbh_linear_glu(_ptr(x), _ptr(w), _ptr(out), M, N, K, limit, alpha, _ptr(rowscale), pitch, group, dt_of(x.dtype), _stream()), "mbh_linear_glu")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ sublayers that read the stream itself
+def canon_conv(x32: torch.Tensor, w: torch.Tensor, state: torch.Tensor, state_off: int, q_start, seqpos, slots, B: int, one_each: bool) -> torch.Tensor:
+    """h = x32 + causal convolution over time of x32 on every channel (w [D, taps]), in the weights' dtype; the sequences' last taps - 1
+    inputs live in `state` (fp32 [rows, ...], this convolution's part at `state_off` floats into a row) and are advanced."""
+    T, D = x32.shape
+    assert x32.dtype == torch.float32 and state.dtype == torch.float32 and w.shape[0] == D
+    h = torch.empty(T, D, dtype=w.dtype, device=x32.device)
+    _check(lib().mbh_canon_conv(_ptr(x32), _ptr(w), _ptr(state), state[0].numel(), state_off, _ptr(q_start), _ptr(seqpos), _ptr(slots), _ptr(h), T, B, D,
+                                w.shape[1], int(one_each), dt_of(w.dtype), _stream()), "mbh_canon_conv")
+    return h
+
+
+def rmsnorm_add(y32: torch.Tensor, w: torch.Tensor, acc32: torch.Tensor, eps: float, stack: Optional[torch.Tensor] = None, n: int = 0,
+                coef: Optional[torch.Tensor] = None, out32: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """acc32 += rms_norm(y32) * w.  With stack (fp32 [>= n, T, D], whose row n - 1 is acc32): out32 = sum_j coef[j] * stack[j]."""
+    T, D = y32.shape
+    assert y32.dtype == torch.float32 and acc32.dtype == torch.float32 and acc32.shape == y32.shape
+    if stack is not None:
+        assert stack.dtype == torch.float32 and coef.numel() == n and coef.dtype == w.dtype and out32.shape == y32.shape
+        assert stack[n - 1].data_ptr() == acc32.data_ptr(), "the last averaged result is the stream that was just updated"
+    _check(lib().mbh_rmsnorm_add(_ptr(y32), _ptr(w), _ptr(acc32), T, D, eps, _ptr(stack), T * D, _ptr(coef), n, _ptr(out32), dt_of(w.dtype), _stream()),
+           "mbh_rmsnorm_add")
+    return acc32
+
+
+def depth_mix(stack: torch.Tensor, n: int, coef: torch.Tensor, out32: torch.Tensor) -> torch.Tensor:
+    """out32 = sum_(j < n) coef[j] * stack[j]; stack fp32 [>= n, T, D]."""
+    assert stack.dtype == torch.float32 and out32.dtype == torch.float32 and coef.numel() == n
+    _check(lib().mbh_depth_mix(_ptr(stack), stack[0].numel(), _ptr(coef), n, _ptr(out32), out32.numel(), dt_of(coef.dtype), _stream()), "mbh_depth_mix")
+    return out32
+
+
+def retention_qab(qk: torch.Tensor, freq: torch.Tensor, decay: torch.Tensor, positions, H: int, d: int, rot_dims: int, kscale: float) -> torch.Tensor:
+    assert freq.dtype == torch.float64 and freq.numel() == rot_dims // 2 and decay.dtype == torch.float32 and decay.numel() == H
+    T = qk.shape[0]
+    qab = torch.empty(T, 3, H * d, dtype=torch.float32, device=qk.device)
+    _check(lib().mbh_retention_qab(_ptr(qk), qk.shape[1], _ptr(freq), _ptr(decay), _ptr(positions), _ptr(qab), T, H, d, rot_dims, kscale, dt_of(qk.dtype),
+                                   _stream()), "mbh_retention_qab")
+    return qab
+
+
+def gla_qab(qk: torch.Tensor, z32: torch.Tensor, Hd: int, qscale: float, inv_tau: float) -> torch.Tensor:
+    T = qk.shape[0]
+    assert z32.dtype == torch.float32 and z32.shape == (T, Hd)
+    qab = torch.empty(T, 3, Hd, dtype=torch.float32, device=qk.device)
+    _check(lib().mbh_gla_qab(_ptr(qk), qk.shape[1], _ptr(z32), _ptr(qab), T, Hd, qscale, inv_tau, dt_of(qk.dtype), _stream()), "mbh_gla_qab")
+    return qab
+
+
+def whole_norm_prep(qkv, qnorm, knorm, cache_rows, ring_k, ring_v, Nq: int, Nk: int, Nv: int, eps: float, own: bool):
+    """(q, k or None, v or None) with q and k RMS-normed over their whole projections; `own`: k and v returned token-major;
+    `cache_rows` given: written into the ring rows."""
+    T = qkv.shape[0]
+    q = torch.empty(T, Nq, dtype=qkv.dtype, device=qkv.device)
+    k = torch.empty(T, Nk, dtype=qkv.dtype, device=qkv.device) if own else None
+    v = torch.empty(T, Nv, dtype=qkv.dtype, device=qkv.device) if own else None
+    _check(lib().mbh_whole_norm_prep(_ptr(qkv), _ptr(qnorm), _ptr(knorm), _ptr(cache_rows), _ptr(q), _ptr(k), _ptr(v), _ptr(ring_k), _ptr(ring_v), T, Nq,
+                                     Nk, Nv, eps, dt_of(qkv.dtype), _stream()), "mbh_whole_norm_prep")
+    return q, k, v
+
+
+def linear_relu2(x: torch.Tensor, w: torch.Tensor, rowscale: Optional[torch.Tensor] = None, group: int = 0) -> torch.Tensor:
+    """max(x W^T, 0)^2, column c multiplied by rowscale[m, c // group] (experts without a gate, run densely)."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and x.dtype == w.dtype
+    pitch = 0
+    if rowscale is not None:
+        assert rowscale.dtype == torch.float32 and rowscale.shape[0] == M and group > 0 and (N + group - 1) // group <= rowscale.shape[1]
+        pitch = rowscale.shape[1]
+    out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    if _prompt_gemm_ok(x, M, N, K):
+        y = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        _abi.linear_residual(x, w, None, y, _workspace(x.device))
+        _check(lib().mbh_relu2_epilogue(_ptr(y), _ptr(out), M, N, _ptr(rowscale), pitch, group, dt_of(x.dtype), _stream()), "mbh_relu2_epilogue")
+        return out
+    _check(lib().mbh_linear_relu2(_ptr(x), _ptr(w), _ptr(out), M, N, K, _ptr(rowscale), pitch, group, dt_of(x.dtype), _stream()), "mbh_linear_relu2")
     return out

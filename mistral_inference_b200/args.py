@@ -273,14 +273,96 @@ class ScaledInputMoeArgs:
         return a
 
 
+@dataclass
+class RetentionArgs:
+    """Linear attention with one fixed decay per head and no normaliser: S <- decay_h S + k v^T, o = S^T q.  Queries and keys are
+    rotated on the first `rot_dims` entries of each head, entry i paired with entry i + rot_dims / 2 (angle position *
+    rot_base^(-2i / rot_dims)); the rotated key is scaled by dim^(-1/2).  fp32 state [heads, dim, vdim] per sequence."""
+    heads: int
+    dim: int
+    vdim: int
+    decay: List[float]
+    rot_base: float = 10000.0
+    rot_dims: int = 0
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "RetentionArgs":
+        rot = d.get("rot") or {}
+        a = cls(heads=int(d["heads"]), dim=int(d["dim"]), vdim=int(d["vdim"]), decay=[float(x) for x in d["decay"]],
+                rot_base=float(rot.get("base", 10000.0)), rot_dims=int(rot.get("dims", d["dim"])) if rot else 0)
+        assert len(a.decay) == a.heads, "one decay per head"
+        assert a.rot_dims <= a.dim and a.rot_dims % 2 == 0, "the rotation covers an even number of a head's entries"
+        return a
+
+
+@dataclass
+class GlaArgs:
+    """Gated linear attention: a decay per key channel, alpha = sigmoid(z)^(1 / tau) with z from a low-rank projection (its rank is
+    the checkpoint's), S <- diag(alpha) S + k v^T, o = S^T (q dim^(-1/2)).  fp32 state [heads, dim, vdim] per sequence."""
+    heads: int
+    dim: int
+    vdim: int
+    tau: float
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "GlaArgs":
+        return cls(heads=int(d["heads"]), dim=int(d["dim"]), vdim=int(d["vdim"]), tau=float(d["tau"]))
+
+
+@dataclass
+class SigmoidAttentionArgs:
+    """Attention without a softmax and without rotation: q and k are RMS-normed over their whole projections, a visible key weighs
+    sigmoid(q.k * scale + a number per head), weights are not normalised; grouped key/value heads, optional sliding window of
+    `window` positions (the token itself included), a sigmoid gate per head on the output; q, k, v and output projections have biases."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: Optional[int] = None
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "SigmoidAttentionArgs":
+        a = cls(heads=int(d["heads"]), kv_heads=int(d["kv_heads"]), dim=int(d["dim"]), vdim=int(d["vdim"]), scale=float(d["scale"]),
+                window=int(d["mask"]["size"]) if d.get("mask") else None)
+        assert a.heads % a.kv_heads == 0, "query heads must be a multiple of key/value heads"
+        assert a.window is None or a.window >= 1
+        return a
+
+
+@dataclass
+class Relu2FfArgs:
+    """Feed-forward without a gate: W_down max(W_up h, 0)^2."""
+    ff: int
+
+
+@dataclass
+class Relu2MoeArgs:
+    """Mixture of experts of the Relu2FfArgs form with an fp32 softmax router over all experts: the `top` largest scores are chosen,
+    weighted by score * router_scale (not renormalised); an optional shared expert runs for every token."""
+    ff: int
+    experts: int
+    top: int
+    router_scale: float = 1.0
+    shared: Optional[Relu2FfArgs] = None
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "Relu2MoeArgs":
+        r, sh = d["router"], d.get("shared")
+        a = cls(ff=int(d["expert"]["ff"]), experts=int(r["experts"]), top=int(r["top"]), router_scale=float(r.get("scale", 1.0)),
+                shared=Relu2FfArgs(ff=int(sh["ff"])) if sh else None)
+        assert 1 <= a.top <= a.experts, "top must be between 1 and the number of experts"
+        return a
+
+
 MLP_ARGS = {"dense": ClampedGluArgs, "moe": MoeFfArgs}
 
 
 @dataclass
 class LayerArgs:
     type: str                                             # a key of MIXER_ARGS
-    mixer: Union[BiasedAttentionArgs, LightningArgs, LatentAttentionArgs, SideBySideArgs, MlstmArgs]
-    mlp: Union[None, ClampedGluArgs, MoeFfArgs, ScaledInputMoeArgs]
+    mixer: Union[BiasedAttentionArgs, LightningArgs, LatentAttentionArgs, SideBySideArgs, MlstmArgs, RetentionArgs, GlaArgs, SigmoidAttentionArgs]
+    mlp: Union[None, ClampedGluArgs, MoeFfArgs, ScaledInputMoeArgs, Relu2MoeArgs]
 
 
 MIXER_ARGS = {"attention": BiasedAttentionArgs, "lightning": LightningArgs, "latent_attention": LatentAttentionArgs,
@@ -299,12 +381,18 @@ class LoopArgs:
 # What a design fixes (not in config.json): the kind of norm, whether each sublayer's output is normed again before it is added
 # to the residual stream, whether mixer and feed-forward of a layer read the same normed input (one norm per layer) and are added
 # together, whether a learned position vector is added to the embedding, and which feed-forward a kind names (default: MLP_ARGS).
+# "pre_norm": False -- the sublayers read the stream itself and norm1 / norm2 act on their OUTPUTS; "canon" -- what a sublayer reads
+# is first replaced by itself plus a causal convolution over time (taps from config "canon"); "depth_average" -- what goes on to the
+# next layer is a learned weighted average of the embedding output and every layer result so far; "tied_head" -- the logits use the
+# embedding table.  DESIGN_MIXER_ARGS: which mixer a type names in a design (default: MIXER_ARGS).
 DESIGNS = {
     "Fesenex": {"norm": "rms", "post_norm": False},
     "Taruvik": {"norm": "layer", "post_norm": True},
     "Lotazen": {"norm": "rms_scalar", "post_norm": False, "parallel_block": True, "learned_positions": True},
+    "Viladra": {"norm": "rms", "post_norm": True, "pre_norm": False, "canon": True, "depth_average": True, "tied_head": True},
 }
-DESIGN_MLP_ARGS = {"Lotazen": {"moe": ScaledInputMoeArgs}}
+DESIGN_MLP_ARGS = {"Lotazen": {"moe": ScaledInputMoeArgs}, "Viladra": {"moe": Relu2MoeArgs}}
+DESIGN_MIXER_ARGS = {"Viladra": {"attention": SigmoidAttentionArgs, "retention": RetentionArgs, "gla": GlaArgs}}
 
 
 @dataclass
@@ -324,6 +412,11 @@ class LayeredArgs:
     learned_positions: bool = False  # x = embed[token] + pos[position]; max_positions rows
     max_positions: int = 0
     logit_softcap: float = 0.0       # > 0: logits <- cap * tanh(logits / cap)
+    pre_norm: bool = True            # False (with post_norm): x <- x + norm(sublayer(x)), norm1 / norm2 on the outputs only
+    canon: bool = False              # sublayers read x + causal_conv(x); canon_taps taps
+    canon_taps: int = 0
+    depth_average: bool = False      # the next layer reads sum_j dwa[j] X_j over the embedding output and the layer results so far
+    tied_head: bool = False          # logits = embed x (the table without its scale)
 
     def layer_runs(self) -> List[int]:
         """The layer index of every layer run, in order (a looped layer appears once per pass)."""
@@ -343,8 +436,13 @@ class LayeredArgs:
         if d["architecture"] not in DESIGNS:
             raise ValueError(f"unknown architecture {d['architecture']!r} (known: {sorted(DESIGNS)})")
         mlp_args = {**MLP_ARGS, **DESIGN_MLP_ARGS.get(d["architecture"], {})}
+        mixer_args = {**MIXER_ARGS, **DESIGN_MIXER_ARGS.get(d["architecture"], {})}
+        design = dict(DESIGNS[d["architecture"]])
+        if design.get("canon"):
+            design["canon_taps"] = int(d["canon"]["taps"])
+            assert design["canon_taps"] >= 1, "canon.taps >= 1"
         for L in d["layers"]:
-            if L["type"] not in MIXER_ARGS:
+            if L["type"] not in mixer_args:
                 raise ValueError(f"unknown mixer type {L['type']!r}")
             mlp = None
             if L.get("mlp") is not None:
@@ -352,7 +450,7 @@ class LayeredArgs:
                 if kind not in mlp_args:
                     raise ValueError(f"unknown feed-forward kind {kind!r}")
                 mlp = mlp_args[kind].from_dict(L["mlp"])
-            layers.append(LayerArgs(type=L["type"], mixer=MIXER_ARGS[L["type"]].from_dict(L["mixer"]), mlp=mlp))
+            layers.append(LayerArgs(type=L["type"], mixer=mixer_args[L["type"]].from_dict(L["mixer"]), mlp=mlp))
         loop = None
         if d.get("loop"):
             lp = d["loop"]
@@ -361,4 +459,4 @@ class LayeredArgs:
         return cls(architecture=d["architecture"], vocab=int(d["vocab"]), width=int(d["width"]),
                    embedding_scale=float((d.get("embedding") or {}).get("scale", 1.0)), norm_eps=float(d["norm"]["eps"]), layers=layers,
                    loop=loop, max_positions=int(d.get("max_positions", 0)), logit_softcap=float(d.get("logit_softcap") or 0.0),
-                   **DESIGNS[d["architecture"]])
+                   **design)

@@ -40,13 +40,16 @@ def get_cache_sizes(n_layers: int, max_seq_len: int, sliding_window: SlidingWind
 class LayerCacheSpec:
     """What one layer keeps per sequence.  kind "ring": keys [W, n_kv_heads, k_dim] and values [W, n_kv_heads, v_dim] in the model
     dtype (window None = the whole sequence).  kind "state": one fp32 tensor of `state_shape`, carried from token to token.  A ring
-    layer with a non-empty `state_shape` keeps both (a layer whose mixer is an attention beside a recurrence)."""
+    layer with a non-empty `state_shape` keeps both (a layer whose mixer is an attention beside a recurrence).  `conv_shape`: beside
+    either, an fp32 tensor with the last inputs of the layer's short convolutions over time (a layer whose sublayers read their
+    input through a causal convolution)."""
     kind: str = "ring"
     n_kv_heads: int = 0
     k_dim: int = 0
     v_dim: int = 0
     window: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
+    conv_shape: Tuple[int, ...] = ()
 
 
 @dataclass
@@ -69,7 +72,8 @@ class CacheView:
     """cache.py:70-137: one layer's ring plus the metadata of this forward."""
 
     def __init__(self, cache_k: Optional[torch.Tensor], cache_v: Optional[torch.Tensor], metadata: CacheInputMetadata, kv_seqlens_host: List[int],
-                 state: Optional[torch.Tensor] = None):
+                 state: Optional[torch.Tensor] = None, conv: Optional[torch.Tensor] = None):
+        self.conv = conv    # fp32 [rows, *conv_shape]: the last inputs of the layer's convolutions over time
         self.cache_k = cache_k
         self.cache_v = cache_v
         self.state = state  # fp32 [rows, *state_shape] of a recurrent layer
@@ -101,6 +105,7 @@ class BufferCache:
         self.max_seq_len = max_seq_len
         self.layer_specs = layer_specs
         self.cache_state: Dict[int, torch.Tensor] = {}
+        self.cache_conv: Dict[int, torch.Tensor] = {}
         self._rows: Optional[List[int]] = None  # physical row block of each live sequence, in batch order
         self.n_kv_heads = n_kv_heads
         self.head_dim = head_dim
@@ -127,6 +132,8 @@ class BufferCache:
             else:
                 assert sp.kind == "state", sp.kind
                 self.cache_state[i] = torch.empty((max_batch_size, *sp.state_shape), dtype=torch.float32)
+            if sp is not None and sp.conv_shape:
+                self.cache_conv[i] = torch.empty((max_batch_size, *sp.conv_shape), dtype=torch.float32)
         # host copy of the valid length per batch element (the reference keeps it on the device and syncs, cache.py:217)
         self._kv_seqlens_host: Optional[List[int]] = None
 
@@ -134,7 +141,7 @@ class BufferCache:
     def get_view(self, layer_id: int, metadata: CacheInputMetadata) -> CacheView:
         assert self._kv_seqlens_host is not None
         return CacheView(self.cache_k.get(layer_id), self.cache_v.get(layer_id), metadata, self._kv_seqlens_host,
-                         state=self.cache_state.get(layer_id))
+                         state=self.cache_state.get(layer_id), conv=self.cache_conv.get(layer_id))
 
     def reset(self) -> None:
         self._kv_seqlens_host = None
@@ -180,6 +187,8 @@ class BufferCache:
             self.cache_v[i] = self.cache_v[i].to(device=device, dtype=dtype)
         for i in self.cache_state:  # recurrent state stays fp32
             self.cache_state[i] = self.cache_state[i].to(device=device)
+        for i in self.cache_conv:
+            self.cache_conv[i] = self.cache_conv[i].to(device=device)
         return self
 
     def update_seqlens(self, seqlens: List[int]) -> None:

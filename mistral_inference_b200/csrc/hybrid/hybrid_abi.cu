@@ -8,6 +8,7 @@
 #include "hybrid_moe.cuh"
 #include "hybrid_rotary.cuh"
 #include "hybrid_gated_scan.cuh"
+#include "hybrid_stream.cuh"
 #include "../../../include/mistral_b200_hybrid.h"
 
 #include <stdio.h>
@@ -101,7 +102,7 @@ template <typename T> static void run_layernorm(const void* x32, const void* w, 
 }
 template <typename T> static void run_attn_wide(const AttnArgs& a, size_t smem, cudaStream_t st) {
     attn_bias_kernel<T, AT_MAXR_WIDE><<<dim3((unsigned)(a.T * a.H), (unsigned)a.splits), AT_WARPS * 32, smem, st>>>(a);
-    if (a.splits > 1) attn_merge_kernel<T><<<dim3((unsigned)(a.T * a.H), (unsigned)((a.e + 127) / 128)), 128, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e);
+    if (a.splits > 1) attn_merge_kernel<T><<<dim3((unsigned)(a.T * a.H), (unsigned)((a.e + 127) / 128)), 128, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e, a.sigmoid);
 }
 template <typename T> static void run_moe_sparse(const MoeSparseArgs& a, int64_t T_, cudaStream_t st) {
     moe_gateup_sparse_kernel<T><<<dim3((unsigned)((a.ff + MOE_WARPS - 1) / MOE_WARPS), (unsigned)(T_ * a.top)), MOE_WARPS * 32, 0, st>>>(a);
@@ -117,7 +118,7 @@ template <typename T> static void run_epilogue(const LinearArgs& a, const void* 
 template <typename T> static void run_prep(const AttnPrepArgs& a, int64_t T_, cudaStream_t st) { attn_prep_kernel<T><<<(unsigned)T_, 128, 0, st>>>(a); }
 template <typename T> static void run_attn(const AttnArgs& a, size_t smem, cudaStream_t st) {
     attn_bias_kernel<T><<<dim3((unsigned)(a.T * a.H), (unsigned)a.splits), AT_WARPS * 32, smem, st>>>(a);
-    if (a.splits > 1) attn_merge_kernel<T><<<dim3((unsigned)(a.T * a.H), (unsigned)((a.e + 127) / 128)), 128, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e);
+    if (a.splits > 1) attn_merge_kernel<T><<<dim3((unsigned)(a.T * a.H), (unsigned)((a.e + 127) / 128)), 128, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e, a.sigmoid);
 }
 template <typename T> static void run_headnorm(const void* o32, const void* w, const void* g, int64_t g_pitch, int64_t g_off, void* y, int64_t T_,
                                                int64_t N, float eps, cudaStream_t st) {
@@ -198,14 +199,15 @@ int mbh_attn_bias(const void* q, const void* cache_k, const void* cache_v, const
                   const void* q_start, const void* slots, void* out, int64_t T, int64_t B, int64_t W, int64_t H, int64_t G, int64_t d, int64_t e,
                   float scale, int64_t n_tiles, int64_t splits, void* scratch, int dt, void* stream) {
     return mbh_attn_window(q, cache_k, cache_v, bias_tab, n_tab, positions, q_start, slots, out, T, B, W, H, G, d, e, scale, n_tiles, splits, scratch,
-                           0, nullptr, nullptr, nullptr, 0, dt, stream);
+                           0, nullptr, nullptr, nullptr, 0, 0, dt, stream);
 }
 
 int mbh_attn_window(const void* q, const void* cache_k, const void* cache_v, const void* bias_tab, int64_t n_tab, const void* positions,
                     const void* q_start, const void* slots, void* out, int64_t T, int64_t B, int64_t W, int64_t H, int64_t G, int64_t d, int64_t e,
                     float scale, int64_t n_tiles, int64_t splits, void* scratch, int64_t window, const void* own_k, const void* own_v,
-                    const void* seqpos, int64_t chunk, int dt, void* stream) {
+                    const void* seqpos, int64_t chunk, int weights, int dt, void* stream) {
     if (T == 0) return 0;
+    if (weights != 0 && weights != 1) return bad("mbh_attn_window: weights are 0 (softmax) or 1 (sigmoid)");
     if (chunk < 0 || chunk > AT_CHUNK) return bad("mbh_attn_window: chunk is 0 (default) or 1 .. 128 keys");
     if (e > 32 * AT_MAXR) return bad("mbh_attn_bias: value size above 256");
     if (H % G) return bad("mbh_attn_bias: heads must be a multiple of kv heads");
@@ -213,7 +215,7 @@ int mbh_attn_window(const void* q, const void* cache_k, const void* cache_v, con
     if (window < 0 || (!own_k != !own_v) || (own_k && !seqpos)) return bad("mbh_attn_window: window >= 0; own keys, own values and seqpos come together");
     AttnArgs a{q, cache_k, cache_v, (const float*)bias_tab, (int)n_tab, (const int*)positions, (const int*)q_start, (const int*)slots, out,
                (int)T, (int)B, (int)W, (int)H, (int)G, (int)d, (int)e, scale, (int)(splits > 1 && scratch ? splits : 1), (float*)scratch, 0, 0,
-               (int)window, own_k, own_v, (const int*)seqpos, (int)chunk};
+               (int)window, own_k, own_v, (const int*)seqpos, (int)chunk, weights};
     const size_t smem = sizeof(float) * ((size_t)d + AT_WARPS * AT_CHUNK + AT_WARPS * (2 + 32 * AT_MAXR));
     cudaStream_t st = (cudaStream_t)stream;
     // prompts in bf16: the tensor-core kernel, when the caller counted the 64-query tiles and the sizes are instantiated
@@ -372,14 +374,14 @@ int mbh_latent_vup(const void* o_lat, const void* w_uv, const void* gate, int64_
 }
 
 int mbh_moe_route(const void* h, const void* w_router, const void* correction, void* dense, void* idx, void* wsel, int64_t T, int64_t width,
-                  int64_t n, int64_t groups, int64_t keep, int64_t top, int score, int dt, void* stream) {
+                  int64_t n, int64_t groups, int64_t keep, int64_t top, int score, float scale, int dt, void* stream) {
     if (T == 0) return 0;
     if (groups < 1 || n % groups || keep < 1 || keep > groups) return bad("mbh_moe_route: groups must divide the routed outputs, 1 <= keep <= groups");
     if (top < 1 || top > n / groups * keep) return bad("mbh_moe_route: top exceeds the eligible outputs");
     const size_t smem = sizeof(float) * (size_t)(2 * n + 2 * groups);
     if (smem > 48 * 1024) return bad("mbh_moe_route: too many routed outputs");
     if (score != 0 && score != 1) return bad("mbh_moe_route: score is 0 (softmax) or 1 (sigmoid)");
-    MoeRouteArgs a{h, w_router, correction, (float*)dense, (int*)idx, (float*)wsel, (int)width, (int)n, (int)groups, (int)keep, (int)top, score};
+    MoeRouteArgs a{h, w_router, correction, (float*)dense, (int*)idx, (float*)wsel, (int)width, (int)n, (int)groups, (int)keep, (int)top, score, scale};
     cudaStream_t st = (cudaStream_t)stream;
     DISPATCH(dt, moe_route_kernel<ST><<<(unsigned)T, MOE_ROUTE_THREADS, smem, st>>>(a));
     cudaError_t e = cudaGetLastError();
@@ -507,15 +509,108 @@ int mbh_mlstm_gates(const void* qkvg, const void* gif, void* gates, void* qab, v
 }
 
 int mbh_scan_post(const void* o32, const void* nq, int64_t d, const void* gates, const void* w, int w_per_head, const void* gate, int64_t g_pitch,
-                  int64_t g_off, void* y, int64_t T, int64_t H, int64_t e, int ones, float eps, int dt, void* stream) {
+                  int64_t g_off, int gate_act, void* y, int64_t T, int64_t H, int64_t e, int ones, float eps, int dt, void* stream) {
     if (T == 0) return 0;
     if (ones && (!gates || !nq)) return bad("mbh_scan_post: a normaliser needs its products and the gates");
-    ScanPostArgs a{(const float*)o32, (const float*)nq, (int)d, (const float*)gates, w, w_per_head, gate, (int)g_pitch, (int)g_off, y, (int)H, (int)e, ones ? 1 : 0, eps};
+    ScanPostArgs a{(const float*)o32, (const float*)nq, (int)d, (const float*)gates, w, w_per_head, gate, (int)g_pitch, (int)g_off, gate_act, y, (int)H, (int)e, ones ? 1 : 0, eps};
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned hb = T < 512 ? (unsigned)((H + 3) / 4) : 1u;
     DISPATCH(dt, scan_post_kernel<ST><<<dim3((unsigned)T, hb), 128, 0, st>>>(a));
     cudaError_t err = cudaGetLastError();
     return err ? fail(err, "mbh_scan_post") : 0;
+}
+
+int mbh_canon_conv(const void* x32, const void* w, void* state, int64_t state_stride, int64_t state_off, const void* q_start, const void* seqpos,
+                   const void* slots, void* h, int64_t T, int64_t B, int64_t D, int64_t taps, int one_each, int dt, void* stream) {
+    if (T == 0) return 0;
+    if (taps < 1 || taps > CANON_MAX_TAPS) return bad("mbh_canon_conv: 1 to 16 taps");
+    if (one_each && T != B) return bad("mbh_canon_conv: one token per sequence means T == B");
+    CanonArgs a{(const float*)x32, w, (float*)state, (int)state_stride, (int)state_off, (const int*)q_start, (const int*)seqpos, (const int*)slots, h,
+                (int)B, (int)D, (int)taps};
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned cb = (unsigned)((D + 255) / 256);
+    if (one_each) {
+        DISPATCH(dt, canon_conv_step_kernel<ST><<<dim3((unsigned)B, cb), 256, 0, st>>>(a));
+    } else {
+        DISPATCH(dt, canon_conv_kernel<ST><<<dim3((unsigned)T, cb), 256, 0, st>>>(a));
+        if (taps > 1) canon_state_kernel<<<dim3((unsigned)B, cb), 256, 0, st>>>(a);
+    }
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_canon_conv") : 0;
+}
+
+int mbh_rmsnorm_add(const void* y32, const void* w, void* acc32, int64_t T, int64_t D, float eps, const void* stack, int64_t stack_stride,
+                    const void* coef, int64_t n, void* out32, int dt, void* stream) {
+    if (T == 0) return 0;
+    if (stack && (!coef || !out32 || n < 1)) return bad("mbh_rmsnorm_add: the depth average needs coefficients and an output");
+    NormAddArgs a{(const float*)y32, w, (float*)acc32, (int)D, eps, (const float*)stack, (size_t)stack_stride, coef, (int)n, (float*)out32};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, rmsnorm_add_kernel<ST><<<(unsigned)T, D >= 1024 ? 256 : 128, 0, st>>>(a));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_rmsnorm_add") : 0;
+}
+
+int mbh_depth_mix(const void* stack, int64_t stack_stride, const void* coef, int64_t n, void* out32, int64_t count, int dt, void* stream) {
+    if (count == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, depth_mix_kernel<ST><<<(unsigned)((count + 255) / 256), 256, 0, st>>>((const float*)stack, (size_t)stack_stride, (const ST*)coef, (int)n,
+                                                                                         (float*)out32, (size_t)count));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_depth_mix") : 0;
+}
+
+int mbh_retention_qab(const void* qk, int64_t pitch, const void* freq, const void* decay, const void* positions, void* qab, int64_t T, int64_t H,
+                      int64_t d, int64_t rot_dims, float kscale, int dt, void* stream) {
+    if (T == 0) return 0;
+    if (rot_dims < 0 || rot_dims > d || (rot_dims & 1)) return bad("mbh_retention_qab: the rotation covers an even number of a head's entries");
+    RetentionQabArgs a{qk, (const double*)freq, (const float*)decay, (const int*)positions, (float*)qab, (int)H, (int)d, (int)pitch, (int)rot_dims, kscale};
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned jb = T < 512 ? (unsigned)((H * d + 255) / 256) : 1u;
+    DISPATCH(dt, retention_qab_kernel<ST><<<dim3((unsigned)T, jb), 256, 0, st>>>(a));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_retention_qab") : 0;
+}
+
+int mbh_gla_qab(const void* qk, int64_t pitch, const void* z32, void* qab, int64_t T, int64_t Hd, float qscale, float inv_tau, int dt, void* stream) {
+    if (T == 0) return 0;
+    GlaQabArgs a{qk, (const float*)z32, (float*)qab, (int)Hd, (int)pitch, qscale, inv_tau};
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned jb = T < 512 ? (unsigned)((Hd + 255) / 256) : 1u;
+    DISPATCH(dt, gla_qab_kernel<ST><<<dim3((unsigned)T, jb), 256, 0, st>>>(a));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_gla_qab") : 0;
+}
+
+int mbh_whole_norm_prep(const void* qkv, const void* qnorm, const void* knorm, const void* cache_rows, void* q_out, void* k_out, void* v_out,
+                        void* ring_k, void* ring_v, int64_t T, int64_t Nq, int64_t Nk, int64_t Nv, float eps, int dt, void* stream) {
+    if (T == 0) return 0;
+    if (cache_rows && (!ring_k || !ring_v)) return bad("mbh_whole_norm_prep: ring rows without a ring");
+    WholeNormPrepArgs a{qkv, qnorm, knorm, (const int*)cache_rows, q_out, k_out, v_out, ring_k, ring_v, (int)Nq, (int)Nk, (int)Nv, eps};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, whole_norm_prep_kernel<ST><<<(unsigned)T, 256, 0, st>>>(a));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_whole_norm_prep") : 0;
+}
+
+int mbh_linear_relu2(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, const void* rowscale, int64_t rs_pitch,
+                     int64_t rs_group, int dt, void* stream) {
+    if (rowscale && rs_group <= 0) return bad("mbh_linear_relu2: rs_group must be positive");
+    LinearArgs a{x, w, nullptr, out, nullptr, (int)M, (int)N, (int)K, EPI_RELU2, 0, 0.f, 0.f, (const float*)rowscale, (int)rs_pitch, (int)rs_group};
+    cudaError_t e = cudaSuccess;
+    DISPATCH(dt, e = launch_linear<ST>(a, (cudaStream_t)stream));
+    return e ? fail(e, "mbh_linear_relu2") : 0;
+}
+
+int mbh_relu2_epilogue(const void* y, void* out, int64_t M, int64_t N, const void* rowscale, int64_t rs_pitch, int64_t rs_group, int dt,
+                       void* stream) {
+    if (M == 0 || N == 0) return 0;
+    if (N & 1) return bad("mbh_relu2_epilogue: N must be even");
+    if (rowscale && rs_group <= 0) return bad("mbh_relu2_epilogue: rs_group must be positive");
+    LinearArgs a{nullptr, nullptr, nullptr, out, nullptr, (int)M, (int)N, 0, EPI_RELU2, 0, 0.f, 0.f, (const float*)rowscale, (int)rs_pitch, (int)rs_group};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, run_epilogue<ST>(a, y, st));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_relu2_epilogue") : 0;
 }
 
 }  // extern "C"

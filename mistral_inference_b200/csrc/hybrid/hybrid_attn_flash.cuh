@@ -4,6 +4,7 @@
 // ring; S = Q K^T with mma.sync.m16n8k16 (Q fragments stay in registers); score = S * scale + bias[min(distance, n_tab - 1), h],
 // causal mask, running (max, sum) per query row in fp32; P is rounded to bf16 and multiplies V on the tensor cores with fp32
 // accumulators.  Query tiles never straddle two sequences; positions inside a tile are consecutive.
+// With AttnArgs::sigmoid the weights are sigmoid(score) (fp32, then bf16 for P V) and nothing is normalised.
 #pragma once
 #include "hybrid_mixers.cuh"
 
@@ -116,14 +117,21 @@ __global__ void __launch_bounds__(128) attn_bias_flash_kernel(AttnArgs a) {
                 s[nt][c] = x0; s[nt][2 + c] = x1;
                 mx0 = fmaxf(mx0, x0); mx1 = fmaxf(mx1, x1);
             }
-        const float mn0 = fmaxf(m0, quad_max(mx0)), mn1 = fmaxf(m1, quad_max(mx1));
-        const float c0 = (mn0 == -INFINITY) ? 1.f : expf(m0 - mn0), c1 = (mn1 == -INFINITY) ? 1.f : expf(m1 - mn1);
+        if (a.sigmoid) {  // weights sigmoid(score), 0 where masked; nothing to rescale
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) s[nt][c] = s[nt][c] == -INFINITY ? 0.f : sigmoid_exact(s[nt][c]);
+        }
+        const float mn0 = a.sigmoid ? 0.f : fmaxf(m0, quad_max(mx0)), mn1 = a.sigmoid ? 0.f : fmaxf(m1, quad_max(mx1));
+        const float c0 = (a.sigmoid || mn0 == -INFINITY) ? 1.f : expf(m0 - mn0), c1 = (a.sigmoid || mn1 == -INFINITY) ? 1.f : expf(m1 - mn1);
         float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                const float e0 = (mn0 == -INFINITY) ? 0.f : expf(s[nt][c] - mn0), e1 = (mn1 == -INFINITY) ? 0.f : expf(s[nt][2 + c] - mn1);
+                const float e0 = a.sigmoid ? s[nt][c] : (mn0 == -INFINITY) ? 0.f : expf(s[nt][c] - mn0);
+                const float e1 = a.sigmoid ? s[nt][2 + c] : (mn1 == -INFINITY) ? 0.f : expf(s[nt][2 + c] - mn1);
                 s[nt][c] = e0; s[nt][2 + c] = e1;
                 ps0 += e0; ps1 += e1;
             }
@@ -143,6 +151,7 @@ __global__ void __launch_bounds__(128) attn_bias_flash_kernel(AttnArgs a) {
         }
     }
     l0 = quad_sum(l0); l1 = quad_sum(l1);
+    if (a.sigmoid) l0 = l1 = 1.f;
     bf16* out = static_cast<bf16*>(a.out);
 #pragma unroll
     for (int ne = 0; ne < E / 8; ++ne) {

@@ -17,8 +17,11 @@
 //   mlstm_m / mlstm_qab   exponential input and forget gates kept in range by a running maximum m (m_0 = 0):
 //                    i = cap tanh(i_pre / cap), f = logsigmoid(cap tanh(f_pre / cap)), m_t = max(f + m_(t-1), i),
 //                    a = exp(f + m_(t-1) - m_t) (one number per head), b = exp(i - m_t) k, q scaled; also exp(-m_t) per token
+//   retention_qab    a fixed decay per head and rotated queries and keys: the first rot_dims entries of each head turn by
+//                    position * freq[i], entry i paired with entry i + rot_dims / 2; a = decay[h], b = rotated k * kscale
+//   gla_qab          a decay per key channel from a projection z: a = sigmoid(z)^(1 / tau) = exp(logsigmoid(z) / tau), q scaled, b = k
 //   scan_post        o / (max(|n . q|, exp(-m)) + 1e-6) when there is a normaliser; every head divided by its root mean square;
-//                    times a weight (per head column, or one set shared by the heads) and an optional sigmoid gate
+//                    times a weight (per head column, one set shared by the heads, or none) and an optional gate (sigmoid or SiLU)
 //
 // Everything here is fp32 except the projections that are read and the activations that are written.
 #pragma once
@@ -263,16 +266,74 @@ __global__ void mlstm_qab_kernel(MlstmGateArgs p) {
     }
 }
 
+// ------------------------------------------------------------------------------------------------ retention and GLA gates
+struct RetentionQabArgs {
+    const void* qk;        // [T, pitch]: q (H*d) | k (H*d) | ...
+    const double* freq;    // [rot_dims / 2]
+    const float* decay;    // [H]
+    const int* positions;  // [T]
+    float* qab;            // [T, 3, H*d]
+    int H, d, pitch, rot_dims;
+    float kscale;
+};
+
+// grid (T, blocks of blockDim entries); a thread per (head, entry of the first half of the rotated part or unrotated entry)
+template <typename T>
+__global__ void retention_qab_kernel(RetentionQabArgs p) {
+    const int t = blockIdx.x, Hd = p.H * p.d, half = p.rot_dims >> 1;
+    const T* row = static_cast<const T*>(p.qk) + (size_t)t * p.pitch;
+    float* out = p.qab + (size_t)t * 3 * Hd;
+    const int pos = p.positions[t];
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < Hd; j += gridDim.y * blockDim.x) {
+        const int h = j / p.d, i = j % p.d;
+        out[Hd + j] = p.decay[h];
+        if (i >= p.rot_dims) {
+            out[j] = to_f(row[j]);
+            out[2 * Hd + j] = to_f(row[Hd + j]) * p.kscale;
+        } else if (i < half) {
+            double sn, cs;
+            sincos((double)pos * p.freq[i], &sn, &cs);
+            const float c = (float)cs, s = (float)sn;
+            const float qu = to_f(row[j]), qv = to_f(row[j + half]), ku = to_f(row[Hd + j]), kv = to_f(row[Hd + j + half]);
+            out[j] = qu * c - qv * s;
+            out[j + half] = qv * c + qu * s;
+            out[2 * Hd + j] = (ku * c - kv * s) * p.kscale;
+            out[2 * Hd + j + half] = (kv * c + ku * s) * p.kscale;
+        }
+    }
+}
+
+struct GlaQabArgs {
+    const void* qk;        // [T, pitch]: q (H*d) | k (H*d) | ...
+    const float* z;        // [T, H*d] fp32 decay projection (bias added)
+    float* qab;            // [T, 3, H*d]
+    int Hd, pitch;
+    float qscale, inv_tau;
+};
+
+template <typename T>
+__global__ void gla_qab_kernel(GlaQabArgs p) {
+    const int t = blockIdx.x;
+    const T* row = static_cast<const T*>(p.qk) + (size_t)t * p.pitch;
+    float* out = p.qab + (size_t)t * 3 * p.Hd;
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < p.Hd; j += gridDim.y * blockDim.x) {
+        out[j] = to_f(row[j]) * p.qscale;
+        out[p.Hd + j] = expf(logsigmoid_exact(p.z[(size_t)t * p.Hd + j]) * p.inv_tau);
+        out[2 * p.Hd + j] = to_f(row[p.Hd + j]);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ after the scan
 struct ScanPostArgs {
     const float* o;        // [T, H * e]
     const float* nq;       // with `ones`: [T, H * d], summed over d to n_t . q_t
     int d;
     const float* gates;    // [T, H, 3] (exp(-m_t) in entry 2) with `ones`, else null
-    const void* w;         // weight: [H*e] (w_per_head) or [e] shared by the heads
+    const void* w;         // weight: [H*e] (w_per_head) or [e] shared by the heads; null: none
     int w_per_head;
-    const void* gate;      // sigmoid gate at gate[t * g_pitch + g_off + h*e + c], or null
+    const void* gate;      // gate at gate[t * g_pitch + g_off + h*e + c], or null
     int g_pitch, g_off;
+    int gate_act;          // 0: times sigmoid(gate); 1: times gate * sigmoid(gate)
     void* y;               // [T, H*e]
     int H, e, ones;
     float eps;
@@ -294,12 +355,12 @@ __global__ void __launch_bounds__(128) scan_post_kernel(ScanPostArgs p) {
         for (int c = lane; c < p.e; c += 32) { const float v = o[c] / den; ss = fmaf(v, v, ss); }
         ss = warp_sum(ss);
         const float inv = 1.f / sqrtf(ss / (float)p.e + p.eps);
-        const T* w = static_cast<const T*>(p.w) + (p.w_per_head ? h * p.e : 0);
+        const T* w = p.w ? static_cast<const T*>(p.w) + (p.w_per_head ? h * p.e : 0) : nullptr;
         const T* g = p.gate ? static_cast<const T*>(p.gate) + (size_t)t * p.g_pitch + p.g_off + h * p.e : nullptr;
         T* y = static_cast<T*>(p.y) + ((size_t)t * p.H + h) * p.e;
         for (int c = lane; c < p.e; c += 32) {
-            float v = o[c] / den * inv * to_f(w[c]);
-            if (g) v *= sigmoid_exact(to_f(g[c]));
+            float v = o[c] / den * inv * (w ? to_f(w[c]) : 1.f);
+            if (g) { const float gv = to_f(g[c]); v *= p.gate_act ? gv * sigmoid_exact(gv) : sigmoid_exact(gv); }
             y[c] = from_f<T>(v);
         }
     }

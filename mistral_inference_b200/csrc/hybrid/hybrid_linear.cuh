@@ -11,6 +11,7 @@
 //   EPI_SWIGLU    out[M, N/2]: interleaved rows as for EPI_GLU: out = silu(gate) * up * rowscale[m, c / rs_group]
 //                 (rowscale fp32 [M, rs_pitch] or null: a mixture of experts run densely, every expert's hidden units scaled by
 //                 the token's routing weight, 0 for an expert that the token did not choose)
+//   EPI_RELU2     out[M, N]    = max(acc, 0)^2 * rowscale[m, n / rs_group]   (plain rows, no gate; rowscale as for EPI_SWIGLU)
 //
 // In bf16 mode the Linear's own output is rounded to bf16 before the epilogue's arithmetic (the rounding point of a bf16
 // Linear); accumulation is fp32 in both modes.
@@ -24,7 +25,7 @@
 
 namespace mbh {
 
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GLU = 2, EPI_F32 = 3, EPI_SWIGLU = 4, EPI_RESIDUAL_SCALED = 5 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GLU = 2, EPI_F32 = 3, EPI_SWIGLU = 4, EPI_RESIDUAL_SCALED = 5, EPI_RELU2 = 6 };
 
 struct LinearArgs {
     const void* x; const void* w; const void* bias;
@@ -70,6 +71,17 @@ __device__ __forceinline__ void epilogue_pair(const LinearArgs& a, int m, int n,
         float v = v0 * sigmoid_exact(v0) * v1;
         if (a.rowscale) v *= a.rowscale[(size_t)m * a.rs_pitch + c / a.rs_group];
         static_cast<T*>(a.out)[(size_t)m * (a.N >> 1) + c] = from_f<T>(v);
+        break; }
+    case EPI_RELU2: {
+        T* o = static_cast<T*>(a.out) + (size_t)m * a.N + n;
+        v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f);
+        v0 *= v0; v1 *= v1;
+        if (a.rowscale) {
+            v0 *= a.rowscale[(size_t)m * a.rs_pitch + n / a.rs_group];
+            if (has1) v1 *= a.rowscale[(size_t)m * a.rs_pitch + (n + 1) / a.rs_group];
+        }
+        o[0] = from_f<T>(v0);
+        if (has1) o[1] = from_f<T>(v1);
         break; }
     default: {
         float* o = a.out32 + (size_t)m * a.N + n;

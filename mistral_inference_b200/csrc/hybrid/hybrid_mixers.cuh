@@ -5,8 +5,10 @@
 //   layernorm_f32     y = (x - mean) / sqrt(var + eps) * w + b          fp32 in; storage type out, or added to the residual stream
 //   attn_prep         per-head RMS norm of q and k (shared weight), query temperature by position, value mixing with an
 //                     earlier layer's values, scatter of k and v into the layer's cache ring
+//   whole_norm_prep   RMS norm of a token's whole query and whole key projection (weights of that size), k and v to the ring
 //   attn_bias         causal softmax attention over the ring with a per-(distance, head) additive bias, GQA, separate
-//                     key and value sizes; one kernel for prompts, prompt portions and decode
+//                     key and value sizes; one kernel for prompts, prompt portions and decode; optionally a sliding window and
+//                     sigmoid weights instead of the softmax (every visible key weighs sigmoid(score), nothing is normalised)
 //   lightning_scan    decayed linear attention S <- a S + k v^T, o = S^T q with the fp32 state carried in the cache
 //   gated_headnorm    y = rms(o over all heads) * w * sigmoid(g)
 #pragma once
@@ -111,6 +113,48 @@ __global__ void attn_prep_kernel(AttnPrepArgs a) {
     }
 }
 
+// ------------------------------------------------------------------------------------------------ attention: norm over the whole projection
+struct WholeNormPrepArgs {
+    const void* qkv;       // [T, H*d + G*d + G*e] projections with bias
+    const void* qnorm;     // [H*d] weight of the RMS norm over ALL query entries of a token (not per head)
+    const void* knorm;     // [G*d] the same for the keys
+    const int* cache_rows; // [T] ring row or -1; null: nothing goes to the ring in this call
+    void* q_out;           // [T, H*d]
+    void* k_out; void* v_out;   // [T, G*d] / [T, G*e] token-major, or null
+    void* ring_k; void* ring_v; // [rows, G, d] / [rows, G, e]
+    int Nq, Nk, Nv;
+    float eps;
+};
+
+// one token per CTA: q <- rms_norm(q) * qnorm and k <- rms_norm(k) * knorm over the whole projections; no rotation
+template <typename T>
+__global__ void __launch_bounds__(256) whole_norm_prep_kernel(WholeNormPrepArgs a) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const T* row = static_cast<const T*>(a.qkv) + (size_t)t * (a.Nq + a.Nk + a.Nv);
+    const int crow = a.cache_rows ? a.cache_rows[t] : -1;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < a.Nq; i += blockDim.x) { const float v = to_f(row[i]); sq = fmaf(v, v, sq); }
+    for (int i = threadIdx.x; i < a.Nk; i += blockDim.x) { const float v = to_f(row[a.Nq + i]); sk = fmaf(v, v, sk); }
+    sq = block_sum(sq, red);
+    sk = block_sum(sk, red);
+    const float iq = 1.f / sqrtf(sq / (float)a.Nq + a.eps), ik = 1.f / sqrtf(sk / (float)a.Nk + a.eps);
+    const T* wq = static_cast<const T*>(a.qnorm);
+    const T* wk = static_cast<const T*>(a.knorm);
+    for (int i = threadIdx.x; i < a.Nq; i += blockDim.x)
+        static_cast<T*>(a.q_out)[(size_t)t * a.Nq + i] = from_f<T>(to_f(row[i]) * iq * to_f(wq[i]));
+    for (int i = threadIdx.x; i < a.Nk; i += blockDim.x) {
+        const T v = from_f<T>(to_f(row[a.Nq + i]) * ik * to_f(wk[i]));
+        if (a.k_out) static_cast<T*>(a.k_out)[(size_t)t * a.Nk + i] = v;
+        if (crow >= 0) static_cast<T*>(a.ring_k)[(size_t)crow * a.Nk + i] = v;
+    }
+    const T* vsrc = row + a.Nq + a.Nk;
+    for (int i = threadIdx.x; i < a.Nv; i += blockDim.x) {
+        if (a.v_out) static_cast<T*>(a.v_out)[(size_t)t * a.Nv + i] = vsrc[i];
+        if (crow >= 0) static_cast<T*>(a.ring_v)[(size_t)crow * a.Nv + i] = vsrc[i];
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ attention core
 struct AttnArgs {
     const void* q;          // [T, H*d]
@@ -134,6 +178,8 @@ struct AttnArgs {
     const int* seqpos;      // [B] tokens cached before this call (with own_k)
     int chunk;              // keys per warp and step, at most AT_CHUNK (0: AT_CHUNK).  A short ring read by few (token, head) pairs -- a decode
                             // step of a small batch over a sliding window -- is spread over more CTAs with a smaller chunk
+    int sigmoid;            // 1: the weight of a visible key is sigmoid(score), not normalised over the keys (no softmax): partial results
+                            // simply add, so the running maximum stays 0 and the sum is never divided by
 };
 
 // where key / value j of a sequence lives: this call's own rows, or the ring
@@ -176,7 +222,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
     const bool vec_ok = (a.d % V == 0) && (ks % V == 0) && (reinterpret_cast<uintptr_t>(a.cache_k) % 16 == 0)
                         && (!a.own_k || reinterpret_cast<uintptr_t>(a.own_k) % 16 == 0);
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;  // first visible key
-    float m = -INFINITY, l = 0.f, acc[MAXR];
+    float m = a.sigmoid ? 0.f : -INFINITY, l = 0.f, acc[MAXR];
 #pragma unroll
     for (int r = 0; r < MAXR; ++r) acc[r] = 0.f;
     const int cpl = (a.e + 31) / 32;  // value columns per lane: lane * cpl .. + cpl - 1
@@ -206,10 +252,10 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
             cmax = fmaxf(cmax, s);
         }
         cmax = warp_max(cmax);
-        const float m_new = fmaxf(m, cmax);
-        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        const float m_new = a.sigmoid ? 0.f : fmaxf(m, cmax);
+        const float corr = a.sigmoid ? 1.f : (m == -INFINITY) ? 0.f : expf(m - m_new);
         float psum = 0.f;
-        for (int jj = lane; jj < cn; jj += 32) { float p = expf(sc[jj] - m_new); sc[jj] = p; psum += p; }
+        for (int jj = lane; jj < cn; jj += 32) { float p = a.sigmoid ? sigmoid_exact(sc[jj]) : expf(sc[jj] - m_new); sc[jj] = p; psum += p; }
         psum = warp_sum(psum);
         l = l * corr + psum;
         m = m_new;
@@ -270,7 +316,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
             T* out = static_cast<T*>(a.out) + ((size_t)t * a.H + h) * a.e;
 #pragma unroll
             for (int r = 0; r < MAXR; ++r)
-                if (r < cpl && lane * cpl + r < a.e) out[lane * cpl + r] = from_f<T>(o[r] / L);
+                if (r < cpl && lane * cpl + r < a.e) out[lane * cpl + r] = from_f<T>(a.sigmoid ? o[r] : o[r] / L);
         }
     }
 }
@@ -280,7 +326,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
 // loads in flight).  grid (token * head, blocks of blockDim columns)
 constexpr int AT_MAX_SPLITS = 64;
 template <typename T>
-__global__ void attn_merge_kernel(const float* __restrict__ scratch, T* __restrict__ out, int splits, int e) {
+__global__ void attn_merge_kernel(const float* __restrict__ scratch, T* __restrict__ out, int splits, int e, int sigmoid = 0) {
     __shared__ float f[AT_MAX_SPLITS];
     __shared__ float red[32];
     const float* part = scratch + (size_t)blockIdx.x * splits * (2 + e);
@@ -293,7 +339,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ scratch, T* __restri
         f[s] = w;
         lpart += w * part[(size_t)s * (2 + e) + 1];
     }
-    const float L = block_sum(lpart, red);  // its barriers also publish f[]
+    const float L = sigmoid ? 1.f : block_sum(lpart, red);  // its barriers also publish f[]
+    if (sigmoid) __syncthreads();
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= e) return;
     const float* col = part + 2 + c;

@@ -26,6 +26,7 @@ struct MoeRouteArgs {
     float* wsel;              // [T, top]
     int width, n, groups, keep, top;
     int score;                // 0: softmax over the outputs; 1: sigmoid of each output
+    float scale;              // the weights (dense and wsel) are the chosen scores times this
 };
 
 // (value, index) argmax over a warp; the lower index wins a tie
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(MoeRouteAr
         warp_argmax(v, ei);
         if (ei == 0x7fffffff) ei = 0;  // fewer eligible outputs than `top` (a configuration error): weight 0 below
         if (lane == 0) {
-            const float w = (v == -INFINITY) ? 0.f : z[ei];
+            const float w = (v == -INFINITY) ? 0.f : z[ei] * a.scale;
             a.idx[(size_t)t * a.top + k] = ei;
             a.wsel[(size_t)t * a.top + k] = w;
             if (v != -INFINITY) { a.dense[(size_t)t * a.n + ei] = w; ch[ei] = -INFINITY; }
@@ -143,7 +144,8 @@ struct MoeSparseArgs {
     float* y32;               // [T, width]
     int width, ff, E, top;
     int glu;                  // 0: silu(gate) * up, the routing weight multiplies the expert's OUTPUT; 1: the weight multiplies the
-    float limit, alpha;       //    expert's INPUT: g = min(w gate, limit), u = clamp(w up, +-limit), act = g sigmoid(alpha g) (u + 1)
+    float limit, alpha;       //    expert's INPUT: g = min(w gate, limit), u = clamp(w up, +-limit), act = g sigmoid(alpha g) (u + 1);
+                              // 2: experts without a gate, act = max(W_up h, 0)^2, w13 = [E * ff, width] plain rows, weight on the OUTPUT
     int accumulate;           // y32 += the experts' sum (y32 is the residual stream) instead of y32 = it
 };
 
@@ -157,11 +159,16 @@ __global__ void __launch_bounds__(MOE_WARPS * 32) moe_gateup_sparse_kernel(MoeSp
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, c = blockIdx.x * MOE_WARPS + warp;
     if (c >= a.ff) return;
     const T* h = static_cast<const T*>(a.h) + (size_t)t * a.width;
+    if (a.glu == 2) {
+        const float u = rnd<T>(warp_dot<T>(static_cast<const T*>(a.w13) + ((size_t)e * a.ff + c) * a.width, h, a.width, lane));
+        if (lane == 0) { const float r = fmaxf(u, 0.f); static_cast<T*>(a.act)[(size_t)slot * a.ff + c] = from_f<T>(r * r); }
+        return;
+    }
     const T* wg = static_cast<const T*>(a.w13) + ((size_t)e * a.ff + c) * 2 * a.width;
     float g = rnd<T>(warp_dot<T>(wg, h, a.width, lane)), u = rnd<T>(warp_dot<T>(wg + a.width, h, a.width, lane));
     if (lane != 0) return;
     float act;
-    if (a.glu) {
+    if (a.glu == 1) {
         const float w = a.wsel[slot];
         g = fminf(g * w, a.limit);
         u = fminf(fmaxf(u * w, -a.limit), a.limit);
@@ -181,7 +188,7 @@ __global__ void __launch_bounds__(MOE_WARPS * 32) moe_down_sparse_kernel(MoeSpar
     float acc = 0.f;
     for (int k = 0; k < a.top; ++k) {
         const int slot = t * a.top + k, e = a.idx[slot];
-        const float w = a.glu ? 1.f : a.wsel[slot];
+        const float w = a.glu == 1 ? 1.f : a.wsel[slot];
         if (e >= a.E) acc += w * to_f(static_cast<const T*>(a.h)[(size_t)t * a.width + n]);
         else acc += w * rnd<T>(warp_dot<T>(wrow + (size_t)e * a.ff, static_cast<const T*>(a.act) + (size_t)slot * a.ff, a.ff, lane));
     }

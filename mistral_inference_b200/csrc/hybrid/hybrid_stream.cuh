@@ -1,0 +1,138 @@
+// Steps on the fp32 residual stream of designs whose sublayers read the stream itself and are normed on the way back:
+//
+//   canon_conv        h[t] = x[t] + sum_j w[:, j] * x[t - taps + 1 + j]: a causal convolution over time on every channel, added to
+//                     its own input; what lies before the sequence's start is zero.  The last taps - 1 inputs of each sequence are
+//                     carried in the cache (fp32), so a prompt portion or a decode step continues where the last call stopped
+//   canon_state       writes those last taps - 1 inputs back after the convolution has read the old ones
+//   canon_conv_step   both for one token per sequence (a decode step), one launch
+//   rmsnorm_add       acc[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w: the norm of a sublayer's OUTPUT, added to the stream in fp32;
+//                     optionally followed by the depth average: out[t] = sum_j c[j] * X_j[t] over the layer results X_0 .. X_(n-1)
+//                     kept one after the other (X_(n-1) is acc itself, just updated)
+//   depth_mix         the depth average alone
+#pragma once
+#include "hybrid_common.cuh"
+
+namespace mbh {
+
+struct CanonArgs {
+    const float* x;        // [T, D] the stream
+    const void* w;         // [D, taps] storage type
+    float* state;          // sequence in slot s: state + s * state_stride + state_off, [taps - 1, D]
+    int state_stride, state_off;
+    const int* q_start;    // [B + 1]
+    const int* seqpos;     // [B] tokens before this call (0: nothing before, whatever the slot holds)
+    const int* slots;      // [B]
+    void* h;               // [T, D] storage type
+    int B, D, taps;
+};
+
+constexpr int CANON_MAX_TAPS = 16;
+
+// grid (T, blocks of channels)
+template <typename T>
+__global__ void canon_conv_kernel(CanonArgs a) {
+    const int t = blockIdx.x;
+    int b = 0;
+    while (b + 1 < a.B && a.q_start[b + 1] <= t) ++b;
+    const int i = t - a.q_start[b], back = a.taps - 1;
+    const bool has_state = a.seqpos[b] > 0;
+    const float* st = a.state + (size_t)a.slots[b] * a.state_stride + a.state_off;
+    const T* W = static_cast<const T*>(a.w);
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < a.D; c += gridDim.y * blockDim.x) {
+        const float xc = a.x[(size_t)t * a.D + c];
+        float acc = 0.f;
+        for (int j = 0; j < a.taps; ++j) {
+            const int src = i - back + j;  // index within this call's tokens of the sequence
+            float v;
+            if (src >= 0) v = a.x[(size_t)(a.q_start[b] + src) * a.D + c];
+            else v = has_state ? st[(size_t)(back + src) * a.D + c] : 0.f;
+            acc = fmaf(to_f(W[(size_t)c * a.taps + j]), v, acc);
+        }
+        static_cast<T*>(a.h)[(size_t)t * a.D + c] = from_f<T>(xc + acc);
+    }
+}
+
+// grid (B, blocks of channels); a thread moves one channel's entries in rising order, reading only entries it has not yet written
+__global__ void canon_state_kernel(CanonArgs a) {
+    const int b = blockIdx.x, back = a.taps - 1;
+    const int len = a.q_start[b + 1] - a.q_start[b];
+    if (len <= 0) return;
+    const bool has_state = a.seqpos[b] > 0;
+    float* st = a.state + (size_t)a.slots[b] * a.state_stride + a.state_off;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < a.D; c += gridDim.y * blockDim.x)
+        for (int j = 0; j < back; ++j) {
+            const int src = len - back + j;
+            float v;
+            if (src >= 0) v = a.x[(size_t)(a.q_start[b] + src) * a.D + c];
+            else v = has_state ? st[(size_t)(j + len) * a.D + c] : 0.f;
+            st[(size_t)j * a.D + c] = v;
+        }
+}
+
+// one token per sequence (token b belongs to sequence b): convolution and state shift in one launch.  grid (B, blocks of channels)
+template <typename T>
+__global__ void canon_conv_step_kernel(CanonArgs a) {
+    const int b = blockIdx.x, back = a.taps - 1;
+    const bool has_state = a.seqpos[b] > 0;
+    float* st = a.state + (size_t)a.slots[b] * a.state_stride + a.state_off;
+    const T* W = static_cast<const T*>(a.w);
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < a.D; c += gridDim.y * blockDim.x) {
+        const float xc = a.x[(size_t)b * a.D + c];
+        float acc = to_f(W[(size_t)c * a.taps + back]) * xc;
+        for (int j = 0; j < back; ++j) {
+            const float v = has_state ? st[(size_t)j * a.D + c] : 0.f;
+            acc = fmaf(to_f(W[(size_t)c * a.taps + j]), v, acc);
+            if (j > 0) st[(size_t)(j - 1) * a.D + c] = v;
+        }
+        if (back > 0) st[(size_t)(back - 1) * a.D + c] = xc;
+        static_cast<T*>(a.h)[(size_t)b * a.D + c] = from_f<T>(xc + acc);
+    }
+}
+
+struct NormAddArgs {
+    const float* y;        // [T, D] sublayer output
+    const void* w;         // [D] storage type
+    float* acc;            // [T, D] the stream, updated in place
+    int D;
+    float eps;
+    const float* stack;    // depth average: X_j = stack + j * stack_stride, j < n - 1; X_(n-1) = acc.  null: none
+    size_t stack_stride;
+    const void* coef;      // [n] storage type
+    int n;
+    float* out;            // [T, D]
+};
+
+// one row per CTA
+template <typename T>
+__global__ void rmsnorm_add_kernel(NormAddArgs a) {
+    __shared__ float red[32];
+    const size_t row = (size_t)blockIdx.x * a.D;
+    const float* r = a.y + row;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < a.D; i += blockDim.x) ss = fmaf(r[i], r[i], ss);
+    ss = block_sum(ss, red);
+    const float inv = 1.f / sqrtf(ss / (float)a.D + a.eps);
+    const T* w = static_cast<const T*>(a.w);
+    const T* cf = static_cast<const T*>(a.coef);
+    for (int i = threadIdx.x; i < a.D; i += blockDim.x) {
+        const float v = a.acc[row + i] + r[i] * inv * to_f(w[i]);
+        a.acc[row + i] = v;
+        if (a.stack) {
+            float m = 0.f;
+            for (int j = 0; j + 1 < a.n; ++j) m = fmaf(to_f(cf[j]), a.stack[(size_t)j * a.stack_stride + row + i], m);
+            a.out[row + i] = fmaf(to_f(cf[a.n - 1]), v, m);
+        }
+    }
+}
+
+// out[i] = sum_j coef[j] * stack[j * stride + i], i < count
+template <typename T>
+__global__ void depth_mix_kernel(const float* __restrict__ stack, size_t stride, const T* __restrict__ coef, int n, float* __restrict__ out, size_t count) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    float m = 0.f;
+    for (int j = 0; j < n; ++j) m = fmaf(to_f(coef[j]), stack[(size_t)j * stride + i], m);
+    out[i] = m;
+}
+
+}  // namespace mbh

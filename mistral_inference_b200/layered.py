@@ -19,7 +19,7 @@ from torch import nn
 from . import _abi, _abi_hybrid as _h
 from .args import LayeredArgs
 from .cache import BufferCache, CacheInputMetadata
-from .transformer_layers import FEED_FORWARDS, MIXERS, BiasedAttention, LayeredBlock, LightningMixer, Norm
+from .transformer_layers import FEED_FORWARDS, MIXERS, MIXERS_BY_ARGS, BiasedAttention, LayeredBlock, LightningMixer, Norm
 
 
 class LayeredTransformer(nn.Module):
@@ -32,18 +32,24 @@ class LayeredTransformer(nn.Module):
         self.embed = nn.Parameter(torch.empty(args.vocab, args.width), requires_grad=False)
         blocks = []
         seen_vmix = False
-        for L in args.layers:
-            if L.type == "attention":
+        assert not (args.depth_average and args.loop is not None), "a depth average over looped layers is not built"
+        for li, L in enumerate(args.layers):
+            if type(L.mixer) in MIXERS_BY_ARGS:
+                mixer = MIXERS_BY_ARGS[type(L.mixer)](args.width, L.mixer, args.norm_eps)
+            elif L.type == "attention":
                 mixer: nn.Module = BiasedAttention(args.width, L.mixer, args.norm_eps, first_vmix=L.mixer.v_mix and not seen_vmix)
                 seen_vmix = seen_vmix or L.mixer.v_mix
             else:
                 mixer = MIXERS[L.type](args.width, L.mixer, args.norm_eps)
             mlp = FEED_FORWARDS[type(L.mlp)](args.width, L.mlp) if L.mlp is not None else None
-            blocks.append(LayeredBlock(args.width, args.norm_eps, mixer, mlp, norm=args.norm, post_norm=args.post_norm, parallel=args.parallel_block))
+            blocks.append(LayeredBlock(args.width, args.norm_eps, mixer, mlp, norm=args.norm, post_norm=args.post_norm, parallel=args.parallel_block,
+                                       pre_norm=args.pre_norm, canon_taps=args.canon_taps if args.canon else 0,
+                                       depth_results=li + 2 if args.depth_average else 0))
         self.layers = nn.ModuleList(blocks)
         self.pos = nn.Parameter(torch.empty(args.max_positions, args.width), requires_grad=False) if args.learned_positions else None
         self.final_norm = Norm(args.width, args.norm_eps, args.norm)
-        self.head = nn.Parameter(torch.empty(args.vocab, args.width), requires_grad=False)
+        # a tied head is the embedding table itself (without the embedding's scale): no parameter of its own
+        self.head = nn.Parameter(torch.empty(args.vocab, args.width), requires_grad=False) if not args.tied_head else None
         self.last_argmax: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ properties
@@ -59,6 +65,8 @@ class LayeredTransformer(nn.Module):
         """The cache of this model, one entry per layer RUN (a layer that runs in several passes keeps each pass's keys apart): a
         whole-sequence ring per attention layer, an fp32 state per lightning layer."""
         specs = [self.layers[i].mix.cache_spec() for i in self.runs]
+        for sp, i in zip(specs, self.runs):
+            sp.conv_shape = self.layers[i].conv_shape()
         cache = BufferCache(len(specs), max_batch_size, max_seq_len, 0, 0, None, layer_specs=specs)
         cache.to(device=self.device, dtype=self.dtype)
         cache.reset()
@@ -96,6 +104,8 @@ class LayeredTransformer(nn.Module):
         else:
             x = _h.embed_scale(input_ids, self.embed, self.args.embedding_scale)
         ctx: Dict[str, torch.Tensor] = {}
+        if self.args.depth_average:
+            return self._run_layers_averaged(x, md, cache, ctx)
         lp = self.args.loop
         first_pass = True
         for r, i in enumerate(self.runs):
@@ -108,11 +118,26 @@ class LayeredTransformer(nn.Module):
                 self._tap(r, x)
         return x
 
+    def _run_layers_averaged(self, x0: torch.Tensor, md: List[CacheInputMetadata], cache: BufferCache, ctx: Dict[str, torch.Tensor]) -> torch.Tensor:
+        """Layers whose input is a weighted average over depth: stack[0] is the embedding output, stack[i + 1] the result of layer i.
+        Layer i works in place on stack[i + 1], which the layer before left holding ITS average (layer 0: a copy of the embedding
+        output); the kernel of the layer's last norm then writes the average over stack[0 .. i + 1] into stack[i + 2], the next layer's
+        stream.  The last slot is what the final norm reads."""
+        n = len(self.runs)
+        stack = torch.empty(n + 2, *x0.shape, dtype=torch.float32, device=x0.device)
+        stack[0].copy_(x0)
+        stack[1].copy_(x0)
+        for r, i in enumerate(self.runs):
+            self.layers[i](stack[r + 1], cache.get_view(r, md[r]), ctx, mix=(stack, stack[r + 2]))
+            if self._tap is not None:
+                self._tap(r, stack[r + 2])
+        return stack[n + 1]
+
     _tap = None  # debugging hook: called with (layer run, residual stream) after every layer run
 
     def logits_of(self, x32: torch.Tensor) -> torch.Tensor:
         """Final norm + head, fp32 [rows, vocab]."""
-        return _h.linear(self.final_norm(x32), self.head, epi=_h.EPI_F32, limit=self.args.logit_softcap)
+        return _h.linear(self.final_norm(x32), self.head if self.head is not None else self.embed, epi=_h.EPI_F32, limit=self.args.logit_softcap)
 
     def _graph_decode_ok(self, seqlens: List[int], cache: Optional[BufferCache]) -> bool:
         if cache is None or self._tap is not None or os.environ.get("MB200_DECODE_GRAPH", "1") == "0":
@@ -204,7 +229,7 @@ class LayeredTransformer(nn.Module):
             return put(self.pos)
         if k == "final.norm.b" and self.final_norm.bias is not None:
             return put(self.final_norm.bias)
-        if k == "head":
+        if k == "head" and self.head is not None:
             return put(self.head)
         lid, rest = k.split(".", 1)
         assert lid[0] == "l" and lid[1:].isdigit() and int(lid[1:]) < self.n_layers, f"Unexpected key {k}"
@@ -216,7 +241,13 @@ class LayeredTransformer(nn.Module):
                 return nrm.load_weight(v)
             if nrm.bias is not None:
                 return put(nrm.bias)
+        if rest in ("canon1", "canon2") and getattr(blk, rest) is not None:
+            return put(getattr(blk, rest).weight)
+        if rest == "dwa" and blk.dwa is not None:
+            return put(blk.dwa)
         part, name = rest.split(".", 1) if "." in rest else (rest, "")
+        if part == "mix" and hasattr(blk.mix, "prepare"):
+            blk.mix.prepare(name, tuple(v.shape))
         if part == "mlp" and blk.mlp is not None and blk.mlp.assign(name, put):
             return None
         m = blk.mix
@@ -249,7 +280,7 @@ class LayeredTransformer(nn.Module):
         def norm_keys(name: str, nrm: Optional[Norm]) -> List[str]:
             return [] if nrm is None else [name] + ([name + ".b"] if nrm.bias is not None else [])
 
-        keys = ["embed", "head"] + norm_keys("final.norm", self.final_norm) + (["pos"] if self.pos is not None else [])
+        keys = ["embed"] + (["head"] if self.head is not None else []) + norm_keys("final.norm", self.final_norm) + (["pos"] if self.pos is not None else [])
         for i, blk in enumerate(self.layers):
             p = f"l{i}."
             for n in ("norm1", "norm1b", "norm2", "norm2b"):
@@ -262,6 +293,7 @@ class LayeredTransformer(nn.Module):
                 keys += [p + "mix." + n for n in blk.mix.checkpoint_names()]
             if blk.mlp is not None:
                 keys += [p + "mlp." + n for n in blk.mlp.checkpoint_names()]
+            keys += [p + n for n in ("canon1", "canon2") if getattr(blk, n) is not None] + ([p + "dwa"] if blk.dwa is not None else [])
         return keys
 
     def load_state_dict(self, state_dict: Any, strict: bool = True, assign: bool = False) -> None:  # type: ignore[override]

@@ -29,6 +29,7 @@ def _reference_format(*a: Any, **k: Any) -> Any:
 register("Fesenex", _layered)
 register("Taruvik", _layered)
 register("Lotazen", _layered)
+register("Viladra", _layered)
 register("transformer", _reference_format)
 
 

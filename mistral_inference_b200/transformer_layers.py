@@ -191,8 +191,8 @@ import math  # noqa: E402
 from typing import Dict  # noqa: E402
 
 from . import _abi_hybrid as _h  # noqa: E402
-from .args import (BiasedAttentionArgs, ClampedGluArgs, Hgrn2Args, LatentAttentionArgs, LightningArgs, MlstmArgs, MoeFfArgs,  # noqa: E402
-                   RotaryAttentionArgs, ScaledInputMoeArgs, SideBySideArgs)
+from .args import (BiasedAttentionArgs, ClampedGluArgs, GlaArgs, Hgrn2Args, LatentAttentionArgs, LightningArgs, MlstmArgs, MoeFfArgs,  # noqa: E402
+                   Relu2FfArgs, Relu2MoeArgs, RetentionArgs, RotaryAttentionArgs, ScaledInputMoeArgs, SideBySideArgs, SigmoidAttentionArgs)
 from .rope import scaled_frequencies  # noqa: E402
 from .cache import LayerCacheSpec  # noqa: E402
 
@@ -204,7 +204,9 @@ MOE_SPARSE_MAX_TOKENS = 16  # up to this many tokens a mixture of experts stream
 class Norm(nn.Module):
     """The norm of a layered decoder: "rms" (weight), "rms_scalar" (ONE number as weight; kept as a vector of equal entries, so the
     same kernel serves it) or "layer" (mean removed; weight and bias).  Reads the fp32 residual stream (or an fp32 sublayer output)
-    and either returns the normed rows in the model dtype or adds them, in fp32, to `add_to`."""
+    and either returns the normed rows in the model dtype or adds them, in fp32, to `add_to`.  `mix` = (stack, n, coef, out), with an
+    rms norm that adds: the depth average out = sum_j coef[j] * stack[j] over the n layer results so far follows in the same kernel
+    (stack[n - 1] is `add_to`)."""
 
     def __init__(self, width: int, eps: float, kind: str):
         super().__init__()
@@ -213,10 +215,13 @@ class Norm(nn.Module):
         self.weight = nn.Parameter(torch.empty(width), requires_grad=False)
         self.bias = nn.Parameter(torch.empty(width), requires_grad=False) if kind == "layer" else None
 
-    def forward(self, x32: torch.Tensor, add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x32: torch.Tensor, add_to: Optional[torch.Tensor] = None, mix: Optional[tuple] = None) -> torch.Tensor:
         if self.kind == "layer":
+            assert mix is None, "a depth average after a layer norm is not built"
             return _h.layernorm(x32, self.weight, self.bias, self.eps, add_to=add_to)
-        assert add_to is None, "an rms norm after the sublayer is not built"
+        if add_to is not None:
+            stack, n, coef, out = mix if mix is not None else (None, 0, None, None)
+            return _h.rmsnorm_add(x32, self.weight, add_to, self.eps, stack, n, coef, out)
         return _h.rmsnorm(x32, self.weight, self.eps)
 
     def load_weight(self, v: torch.Tensor) -> None:
@@ -229,16 +234,17 @@ class Norm(nn.Module):
             self.weight.copy_(v)
 
 
-def project_out(y: torch.Tensor, w: torch.Tensor, x32: torch.Tensor, post: Optional[Norm], scale: float = 1.0) -> None:
+def project_out(y: torch.Tensor, w: torch.Tensor, x32: torch.Tensor, post, scale: float = 1.0, bias: Optional[torch.Tensor] = None) -> None:
     """The last Linear of a sublayer: added to the fp32 residual stream by its epilogue (times `scale`, for a sublayer that enters a
-    weighted sum), or, when the block norms the sublayer's output first (`post`), written in fp32 and added by the norm kernel."""
+    weighted sum), or, when the block norms the sublayer's output first (`post`, called as post(fp32 rows, add_to=stream)), written in
+    fp32 and added by the norm kernel."""
     if post is None and scale != 1.0:
-        _h.linear(y, w, epi=_h.EPI_RESIDUAL_SCALED, residual=x32, alpha=scale)
+        _h.linear(y, w, bias, epi=_h.EPI_RESIDUAL_SCALED, residual=x32, alpha=scale)
     elif post is None:
-        _h.linear(y, w, epi=_h.EPI_RESIDUAL, residual=x32)
+        _h.linear(y, w, bias, epi=_h.EPI_RESIDUAL, residual=x32)
     else:
         assert scale == 1.0, "a scaled sublayer with a norm after it is not built"
-        post(_h.linear(y, w, epi=_h.EPI_F32), add_to=x32)
+        post(_h.linear(y, w, bias, epi=_h.EPI_F32), add_to=x32)
 
 
 def distance_buckets(rows: int, far: float) -> List[int]:
@@ -754,29 +760,344 @@ class ScaledInputMoe(nn.Module):
         return True
 
 
+class RetentionMixer(nn.Module):
+    """Linear attention with a fixed decay per head, rotated queries and keys and no normaliser (args.RetentionArgs): per head
+    S <- decay_h S + (rot(k) dim^(-1/2)) v^T, o = S^T rot(q) in fp32 (state in the cache), every head divided by its root mean square
+    (no weight), times silu(W_g h).  The rotation and the key scale are fp32 steps between the projections and the scan; the scan is
+    the gated one with a_t = decay_h.  Packed weights: wqkvg = q ++ k ++ v ++ g rows."""
+
+    def __init__(self, width: int, a: RetentionArgs, eps: float):
+        super().__init__()
+        self.a, self.eps = a, eps
+        self.nqk, self.nv = a.heads * a.dim, a.heads * a.vdim
+        self.wqkvg = nn.Parameter(torch.empty(2 * self.nqk + 2 * self.nv, width), requires_grad=False)
+        self.wo = nn.Parameter(torch.empty(width, self.nv), requires_grad=False)
+        self._freq: Optional[torch.Tensor] = None
+        self._decay: Optional[torch.Tensor] = None
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="state", state_shape=(self.a.heads, self.a.dim, self.a.vdim))
+
+    def constants(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(float64 [rot_dims / 2] frequencies rot_base^(-2i / rot_dims), fp32 [heads] decays), made on the host once per device."""
+        if self._freq is None or self._freq.device != self.wo.device:
+            f = scaled_frequencies(self.a.rot_dims, self.a.rot_base, None)[0] if self.a.rot_dims else torch.zeros(0, dtype=torch.float64)
+            self._freq = f.to(self.wo.device)
+            self._decay = torch.tensor(self.a.decay, dtype=torch.float32, device=self.wo.device)
+        return self._freq, self._decay
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor], post=None, scale: float = 1.0) -> None:
+        a, md = self.a, view.metadata
+        freq, decay = self.constants()
+        qkvg = _h.linear(hn, self.wqkvg)
+        qab = _h.retention_qab(qkvg, freq, decay, md.positions, a.heads, a.dim, a.rot_dims, a.dim ** -0.5)
+        o32 = _h.gated_scan(qab, qkvg, qkvg.shape[1], 2 * self.nqk, view.state, md.q_start, md.seqpos, md.slots, len(md.seqlens), a.heads, a.dim, a.vdim,
+                            ones=False, max_seqlen=md.max_seqlen)
+        y = _h.scan_post(o32, None, None, False, qkvg, qkvg.shape[1], 2 * self.nqk + self.nv, a.heads, a.vdim, False, self.eps, silu_gate=True)
+        project_out(y, self.wo, x32, post, scale)
+
+    def checkpoint_names(self) -> List[str]:
+        return ["q", "k", "v", "g", "o"]
+
+    def assign(self, name: str, put) -> bool:
+        o = [0, self.nqk, 2 * self.nqk, 2 * self.nqk + self.nv, 2 * self.nqk + 2 * self.nv]
+        idx = {"q": 0, "k": 1, "v": 2, "g": 3}
+        if name in idx:
+            put(self.wqkvg[o[idx[name]]: o[idx[name] + 1]])
+        elif name == "o":
+            put(self.wo)
+        else:
+            return False
+        return True
+
+
+class GlaMixer(nn.Module):
+    """Gated linear attention (args.GlaArgs): a decay per key channel alpha = sigmoid(z)^(1 / tau), z = W_a2 (W_a1 h) + b (fp32 out of
+    the second Linear); per head S <- diag(alpha) S + k v^T, o = S^T (q dim^(-1/2)) in fp32 (state in the cache); every head RMS-normed
+    with one weight [vdim] shared by the heads, times silu(W_g h).  Packed weights: wqkvg = q ++ k ++ v ++ g rows; the rank of the
+    decay projection comes with the checkpoint."""
+
+    def __init__(self, width: int, a: GlaArgs, eps: float):
+        super().__init__()
+        self.a, self.eps, self.width = a, eps, width
+        self.nqk, self.nv = a.heads * a.dim, a.heads * a.vdim
+        self.wqkvg = nn.Parameter(torch.empty(2 * self.nqk + 2 * self.nv, width), requires_grad=False)
+        self.wa1 = nn.Parameter(torch.empty(1, width), requires_grad=False)       # resized by the loader to the checkpoint's rank
+        self.wa2 = nn.Parameter(torch.empty(self.nqk, 1), requires_grad=False)
+        self.ba2 = nn.Parameter(torch.empty(self.nqk), requires_grad=False)
+        self.norm = nn.Parameter(torch.empty(a.vdim), requires_grad=False)
+        self.wo = nn.Parameter(torch.empty(width, self.nv), requires_grad=False)
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="state", state_shape=(self.a.heads, self.a.dim, self.a.vdim))
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor], post=None, scale: float = 1.0) -> None:
+        a, md = self.a, view.metadata
+        qkvg = _h.linear(hn, self.wqkvg)
+        z32 = _h.linear(_h.linear(hn, self.wa1), self.wa2, self.ba2, epi=_h.EPI_F32)
+        qab = _h.gla_qab(qkvg, z32, self.nqk, a.dim ** -0.5, 1.0 / a.tau)
+        o32 = _h.gated_scan(qab, qkvg, qkvg.shape[1], 2 * self.nqk, view.state, md.q_start, md.seqpos, md.slots, len(md.seqlens), a.heads, a.dim, a.vdim,
+                            ones=False, max_seqlen=md.max_seqlen)
+        y = _h.scan_post(o32, None, self.norm, False, qkvg, qkvg.shape[1], 2 * self.nqk + self.nv, a.heads, a.vdim, False, self.eps, silu_gate=True)
+        project_out(y, self.wo, x32, post, scale)
+
+    def checkpoint_names(self) -> List[str]:
+        return ["q", "k", "v", "g", "a1", "a2", "a2.b", "norm", "o"]
+
+    def prepare(self, name: str, shape: Tuple[int, ...]) -> None:
+        """Called by the loader before `assign`: the decay projection takes the rank of the checkpoint's tensors."""
+        if name == "a1" and len(shape) == 2 and shape[1] == self.width and tuple(shape) != tuple(self.wa1.shape):
+            self.wa1 = nn.Parameter(torch.empty(tuple(shape), dtype=self.wa1.dtype, device=self.wa1.device), requires_grad=False)
+        if name == "a2" and len(shape) == 2 and shape[0] == self.nqk and tuple(shape) != tuple(self.wa2.shape):
+            self.wa2 = nn.Parameter(torch.empty(tuple(shape), dtype=self.wa2.dtype, device=self.wa2.device), requires_grad=False)
+
+    def assign(self, name: str, put) -> bool:
+        o = [0, self.nqk, 2 * self.nqk, 2 * self.nqk + self.nv, 2 * self.nqk + 2 * self.nv]
+        idx = {"q": 0, "k": 1, "v": 2, "g": 3}
+        if name in idx:
+            put(self.wqkvg[o[idx[name]]: o[idx[name] + 1]])
+        elif name == "a1":
+            put(self.wa1)
+        elif name == "a2":
+            put(self.wa2)
+        elif name == "a2.b":
+            put(self.ba2)
+        elif name == "norm":
+            put(self.norm)
+        elif name == "o":
+            put(self.wo)
+        else:
+            return False
+        return True
+
+
+class SigmoidWindowAttention(nn.Module):
+    """Attention with sigmoid weights (args.SigmoidAttentionArgs): q and k RMS-normed over their whole projections (weights of that
+    size), no rotation, a visible key weighs sigmoid(q.k * scale + pb[h]) with nothing normalised over the keys, grouped key/value
+    heads, an optional sliding window, head h's output times sigmoid(W_g h)_h; q, k, v and o have biases.  The ring and the order of
+    attention and ring writes are those of RotaryWindowAttention.  Packed weights: wqkvg = q ++ k ++ v ++ g rows (the gate's bias 0)."""
+
+    def __init__(self, width: int, a: SigmoidAttentionArgs, eps: float):
+        super().__init__()
+        self.a, self.eps = a, eps
+        self.nq, self.nk, self.nv = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim
+        self.wqkv = nn.Parameter(torch.empty(self.nq + self.nk + self.nv, width), requires_grad=False)
+        self.bqkv = nn.Parameter(torch.empty(self.nq + self.nk + self.nv), requires_grad=False)
+        self.wg = nn.Parameter(torch.empty(a.heads, width), requires_grad=False)
+        self.q_norm = nn.Parameter(torch.empty(self.nq), requires_grad=False)
+        self.k_norm = nn.Parameter(torch.empty(self.nk), requires_grad=False)
+        self.pb = nn.Parameter(torch.empty(a.heads), requires_grad=False)
+        self.wo = nn.Parameter(torch.empty(width, a.heads * a.vdim), requires_grad=False)
+        self.bo = nn.Parameter(torch.empty(width), requires_grad=False)
+        self._pb32: Optional[torch.Tensor] = None
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="ring", n_kv_heads=self.a.kv_heads, k_dim=self.a.dim, v_dim=self.a.vdim, window=self.a.window)
+
+    def head_bias(self) -> torch.Tensor:
+        if self._pb32 is None or self._pb32.device != self.pb.device:
+            self._pb32 = self.pb.detach().float().contiguous()
+        return self._pb32
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor], post=None, scale: float = 1.0) -> None:
+        a, md = self.a, view.metadata
+        T, B, W = hn.shape[0], len(md.seqlens), md.window
+        qkv = _h.linear(hn, self.wqkv, self.bqkv)
+        gate = _h.linear(hn, self.wg)
+        out = torch.empty(T, a.heads * a.vdim, dtype=hn.dtype, device=hn.device)
+        window = a.window or 0
+        if md.prefill:
+            q, k, v = _h.whole_norm_prep(qkv, self.q_norm, self.k_norm, None, None, None, self.nq, self.nk, self.nv, self.eps, own=True)
+            _h.attn_window(q, view.cache_k, view.cache_v, md.positions, md.q_start, md.slots, out, B, W, a.heads, a.kv_heads, a.dim, a.vdim, a.scale,
+                           window, own_k=k, own_v=v, seqpos=md.seqpos, head_bias=self.head_bias(),
+                           n_tiles=sum((n + 63) // 64 for n in md.seqlens) if md.max_seqlen >= FLASH_MIN_QUERIES else 0)
+            _h.kv_scatter(k, v, md.cache_rows, view.cache_k, view.cache_v)
+        else:
+            q, _, _ = _h.whole_norm_prep(qkv, self.q_norm, self.k_norm, md.cache_rows, view.cache_k, view.cache_v, self.nq, self.nk, self.nv, self.eps,
+                                         own=False)
+            splits, chunk = _h.window_decode_plan(T, a.heads, W)
+            _h.attn_window(q, view.cache_k, view.cache_v, md.positions, md.q_start, md.slots, out, B, W, a.heads, a.kv_heads, a.dim, a.vdim, a.scale,
+                           window, splits=splits, chunk=chunk, head_bias=self.head_bias())
+        _h.head_gate(out, gate, a.heads, 0, a.heads, a.vdim)
+        project_out(out, self.wo, x32, post, scale, bias=self.bo)
+
+    def checkpoint_names(self) -> List[str]:
+        return ["q", "q.b", "k", "k.b", "v", "v.b", "q.norm", "k.norm", "pb", "g", "o", "o.b"]
+
+    def assign(self, name: str, put) -> bool:
+        spans = {"q": (0, self.nq), "k": (self.nq, self.nq + self.nk), "v": (self.nq + self.nk, self.nq + self.nk + self.nv)}
+        direct = {"q.norm": "q_norm", "k.norm": "k_norm", "g": "wg", "o": "wo", "o.b": "bo"}
+        if name in spans:
+            put(self.wqkv[spans[name][0]: spans[name][1]])
+        elif name.endswith(".b") and name[:-2] in spans:
+            put(self.bqkv[spans[name[:-2]][0]: spans[name[:-2]][1]])
+        elif name == "pb":
+            put(self.pb)
+            self._pb32 = None
+        elif name in direct:
+            put(getattr(self, direct[name]))
+        else:
+            return False
+        return True
+
+
+class Relu2FeedForward(nn.Module):
+    """Feed-forward without a gate, W_down max(W_up h, 0)^2 (args.Relu2FfArgs); the square of the rectifier is the epilogue of the
+    first Linear.  `run` adds into `y32` (an fp32 sum of sublayer parts) or, with `post`, norms its own output into the stream."""
+
+    def __init__(self, width: int, a: Relu2FfArgs):
+        super().__init__()
+        self.a, self.width = a, width
+        self.w_up = nn.Parameter(torch.empty(a.ff, width), requires_grad=False)
+        self.w_down = nn.Parameter(torch.empty(width, a.ff), requires_grad=False)
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, post=None) -> None:
+        project_out(_h.linear_relu2(hn, self.w_up), self.w_down, x32, post)
+
+    def checkpoint_names(self) -> List[str]:
+        return ["up", "down"]
+
+    def assign(self, name: str, put) -> bool:
+        if name == "up":
+            put(self.w_up)
+        elif name == "down":
+            put(self.w_down)
+        else:
+            return False
+        return True
+
+
+class Relu2Moe(nn.Module):
+    """Mixture of ungated experts W_down max(W_up h, 0)^2 (args.Relu2MoeArgs): fp32 softmax router over all experts, the `top` largest
+    scores chosen, weights score * router_scale (not renormalised), plus a shared expert for every token.  Packed weights: w_up
+    [E * ff, width], expert after expert; w2 [width, E * ff], expert e's down projection in columns e*ff ..  Few tokens (decode) stream
+    only the chosen experts; prompts run all experts as two Linears, the first one's epilogue scaling every expert's hidden units by
+    the token's routing weight (0 when not chosen).  The parts are summed in fp32 before the norm that follows."""
+
+    def __init__(self, width: int, a: Relu2MoeArgs):
+        super().__init__()
+        self.a, self.width = a, width
+        self.router = nn.Parameter(torch.empty(a.experts, width), requires_grad=False)
+        self.w_up = nn.Parameter(torch.empty(a.experts * a.ff, width), requires_grad=False)
+        self.w2 = nn.Parameter(torch.empty(width, a.experts * a.ff), requires_grad=False)
+        self.shared = Relu2FeedForward(width, a.shared) if a.shared is not None else None
+        self.sparse_max_tokens = MOE_SPARSE_MAX_TOKENS
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, post=None) -> None:
+        a = self.a
+        dense, idx, wsel = _h.moe_route(hn, self.router, None, 1, 1, a.top, score=0, scale=a.router_scale)
+        if hn.shape[0] <= self.sparse_max_tokens:
+            y32 = _h.moe_sparse(hn, self.w_up, self.w2, idx, wsel, a.experts, a.ff, glu=2)
+        else:
+            y32 = _h.linear(_h.linear_relu2(hn, self.w_up, rowscale=dense, group=a.ff), self.w2, epi=_h.EPI_F32)
+        if self.shared is not None:
+            self.shared.run(hn, y32)
+        if post is None:
+            x32.add_(y32)
+        else:
+            post(y32, add_to=x32)
+
+    def checkpoint_names(self) -> List[str]:
+        names = ["router"] + [f"e{e}.{n}" for e in range(self.a.experts) for n in ("up", "down")]
+        return names + (["shared." + n for n in self.shared.checkpoint_names()] if self.shared is not None else [])
+
+    def assign(self, name: str, put) -> bool:
+        a = self.a
+        head, _, part = name.partition(".")
+        if name == "router":
+            put(self.router)
+        elif head == "shared" and self.shared is not None:
+            return self.shared.assign(part, put)
+        elif head[:1] == "e" and head[1:].isdigit() and int(head[1:]) < a.experts:
+            e = int(head[1:])
+            if part == "up":
+                put(self.w_up[e * a.ff: (e + 1) * a.ff])
+            elif part == "down":
+                put(self.w2.view(self.width, a.experts, a.ff)[:, e])
+            else:
+                return False
+        else:
+            return False
+        return True
+
+
+class CanonConv(nn.Module):
+    """What a sublayer reads, replaced by itself plus a causal convolution over time on every channel: h_t = x_t + sum_j w[:, j]
+    x_(t - taps + 1 + j), zeros before the sequence's start.  Reads the fp32 stream, writes the model dtype.  The last taps - 1 inputs
+    of every sequence are part `index` of the layer's convolution state in the cache."""
+
+    def __init__(self, width: int, taps: int, index: int):
+        super().__init__()
+        self.width, self.taps, self.index = width, taps, index
+        self.weight = nn.Parameter(torch.empty(width, taps), requires_grad=False)
+
+    def forward(self, x32: torch.Tensor, view: CacheView) -> torch.Tensor:
+        md = view.metadata
+        return _h.canon_conv(x32, self.weight, view.conv, self.index * (self.taps - 1) * self.width, md.q_start, md.seqpos, md.slots, len(md.seqlens),
+                             one_each=not md.prefill)
+
+
 MIXERS = {"attention": BiasedAttention, "lightning": LightningMixer, "latent_attention": LatentAttention, "parallel": SideBySideMixer,
           "mlstm": MlstmMixer, "mlstm_2": MlstmMixer}
-FEED_FORWARDS = {ClampedGluArgs: ClampedGLU, MoeFfArgs: MoeFeedForward, ScaledInputMoeArgs: ScaledInputMoe}
+# mixers that a design names with a type another design uses differently are found by their argument class first
+MIXERS_BY_ARGS = {RetentionArgs: RetentionMixer, GlaArgs: GlaMixer, SigmoidAttentionArgs: SigmoidWindowAttention}
+FEED_FORWARDS = {ClampedGluArgs: ClampedGLU, MoeFfArgs: MoeFeedForward, ScaledInputMoeArgs: ScaledInputMoe, Relu2MoeArgs: Relu2Moe}
+
+
+class _PostNorm:
+    """The norm after a sublayer as the sublayers call it, post(fp32 rows, add_to=stream), with the depth average that follows the
+    layer's last sublayer."""
+
+    def __init__(self, norm: Norm, mix: Optional[tuple]):
+        self.norm, self.mix = norm, mix
+
+    def __call__(self, y32: torch.Tensor, add_to: torch.Tensor) -> torch.Tensor:
+        return self.norm(y32, add_to=add_to, mix=self.mix)
 
 
 class LayeredBlock(nn.Module):
     """x <- x + mixer(norm1(x)); x <- x + ff(norm2(x)) when the layer has a feed-forward; with `post_norm` each sublayer's output
     goes through a norm of its own (norm1b, norm2b) before it is added.  `parallel`: one norm, h = norm1(x), and both sublayers read
-    it: x <- x + mixer(h) + ff(h).  `x32` is updated in place."""
+    it: x <- x + mixer(h) + ff(h).  Without `pre_norm` (and with `post_norm`) the sublayers read the stream itself and norm1 / norm2
+    act on their outputs: x <- x + norm1(mixer(x)), x <- x + norm2(ff(x)).  `canon_taps` > 0: what a sublayer reads (normed or not) is
+    first replaced by itself plus a causal convolution over time (canon1 for the mixer, canon2 for the feed-forward; their last inputs
+    are the layer's convolution state in the cache).  `depth_results` = n > 0: the block holds n weights `dwa` and, given
+    `mix` = (stack, out), leaves in `out` the weighted average of stack[0 .. n-1], whose last entry is this layer's result.
+    `x32` is updated in place."""
 
     def __init__(self, width: int, eps: float, mixer: nn.Module, mlp: Optional[nn.Module], norm: str = "rms", post_norm: bool = False,
-                 parallel: bool = False):
+                 parallel: bool = False, pre_norm: bool = True, canon_taps: int = 0, depth_results: int = 0):
         super().__init__()
         assert not (parallel and post_norm), "a parallel block with norms after the sublayers is not built"
-        self.eps, self.parallel = eps, parallel
-        self.norm1 = Norm(width, eps, norm)
-        self.norm1b = Norm(width, eps, norm) if post_norm else None
+        assert pre_norm or (post_norm and not parallel and canon_taps > 0), "sublayers that read the stream itself: norms after them, through a convolution"
+        self.eps, self.parallel, self.pre_norm, self.width = eps, parallel, pre_norm, width
+        self.norm1 = Norm(width, eps, norm)  # before the mixer; without pre_norm: after it
+        self.norm1b = Norm(width, eps, norm) if post_norm and pre_norm else None
         self.mix = mixer
         self.mlp = mlp
         self.norm2 = Norm(width, eps, norm) if mlp is not None and not parallel else None
-        self.norm2b = Norm(width, eps, norm) if mlp is not None and post_norm else None
+        self.norm2b = Norm(width, eps, norm) if mlp is not None and post_norm and pre_norm else None
+        assert canon_taps == 0 or not pre_norm, "a convolution after a norm is not built"
+        self.canon1 = CanonConv(width, canon_taps, 0) if canon_taps > 0 else None
+        self.canon2 = CanonConv(width, canon_taps, 1) if canon_taps > 0 and mlp is not None else None
+        self.depth_results = depth_results
+        self.dwa = nn.Parameter(torch.empty(depth_results), requires_grad=False) if depth_results > 0 else None
 
-    def forward(self, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor]) -> torch.Tensor:
+    def conv_shape(self) -> Tuple[int, ...]:
+        """fp32 numbers per sequence that the block's convolutions carry: [convolutions, taps - 1, width]."""
+        if self.canon1 is None or self.canon1.taps < 2:
+            return ()
+        return (1 + int(self.canon2 is not None), self.canon1.taps - 1, self.width)
+
+    def forward(self, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor], mix: Optional[tuple] = None) -> torch.Tensor:
+        if not self.pre_norm:
+            m = (mix[0], self.depth_results, self.dwa, mix[1]) if mix is not None else None
+            last_is_mixer = self.mlp is None
+            self.mix.run(self.canon1(x32, view), x32, view, ctx, _PostNorm(self.norm1, m if last_is_mixer else None))
+            if self.mlp is not None:
+                self.mlp.run(self.canon2(x32, view), x32, _PostNorm(self.norm2, m))
+            return x32
+        assert mix is None, "the depth average follows a norm that adds to the stream"
         if self.parallel:  # the sublayers read hn only, so each may add its output to the stream as it finishes
             hn = self.norm1(x32)
             self.mix.run(hn, x32, view, ctx, None)
