@@ -588,7 +588,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--no-sharded", action="store_true")
-    ap.add_argument("--design", default=None, choices=["fesenex", "taruvik", "lotazen"],
+    ap.add_argument("--design", default=None, choices=["fesenex", "taruvik", "lotazen", "viladra"],
                     help="instead of the default workload: the layered decoder beside the dense transformer of equal size (bench_layered.py)")
     a = ap.parse_args()
 

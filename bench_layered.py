@@ -1,9 +1,11 @@
-"""`bench.py --design fesenex|taruvik|lotazen`: prefill and decode throughput of the layered decoder at layer sizes of real models (random
+"""`bench.py --design fesenex|taruvik|lotazen|viladra`: prefill and decode throughput of the layered decoder at layer sizes of real models (random
 weights), beside the dense `Transformer` of equal width / heads / feed-forward size / depth / vocabulary, plus the time of each
 hybrid kernel at those shapes against its roofline (bf16 tensor peak or HBM copy bandwidth from MEASURED_PEAKS.json).
 For `taruvik` (latent attention, mixture of experts) the neighbour is the `Transformer` with a mixture of experts of equal
 width / heads / experts / depth; for `lotazen` (rotary window attention beside a gated recurrence, matrix memories, experts with scaled
-input) it is the Fesenex design at equal width / heads / depth, and every new kernel is timed next to the like kernel at the same shape.  Timed with CUDA events after warm-up; the prompt batch and the weights exceed L2 at the larger size, and L2 is flushed between
+input) it is the Fesenex design at equal width / heads / depth, and every new kernel is timed next to the like kernel at the same shape;
+for `viladra` (convolution on the stream, norms after the sublayers with a depth average, retention, gated linear attention,
+sigmoid-weight window attention, ungated experts) the neighbour is the Lotazen design at equal width / heads / experts / depth.  Timed with CUDA events after warm-up; the prompt batch and the weights exceed L2 at the larger size, and L2 is flushed between
 timed kernel launches.  Prints one JSON line."""
 import json
 import math
@@ -538,8 +540,214 @@ def run_lotazen(a, peaks: dict) -> dict:
                               "seconds": round(time.time() - t0, 1)}
     return res
 
+# ----------------------------------------------------------------------------------------------- Viladra
+VILADRA_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, rec_heads=16, experts=16, top=2, ff=1408, shared_ff=2816, vocab=32768,
+                  order="grag", rank=64, taps=4),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, window=2048, rec_heads=32, experts=8, top=2, ff=3584, shared_ff=7168, vocab=32768,
+                  order="ar", rank=128, taps=4),
+}
+
+
+def viladra_config(s: dict) -> dict:
+    d, RH = s["dim"], s["rec_heads"]
+    mixers = {
+        "a": {"type": "attention", "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": s["window"]}}},
+        "r": {"type": "retention", "mixer": {"heads": RH, "dim": d, "vdim": d, "decay": [1.0 - 2.0 ** (-5 - 5 * i / max(RH - 1, 1)) for i in range(RH)],
+                                             "rot": {"base": 500000.0, "dims": d}}},
+        "g": {"type": "gla", "mixer": {"heads": RH, "dim": d, "vdim": d, "tau": 16.0}},
+    }
+    mlp = {"kind": "moe", "expert": {"ff": s["ff"]}, "router": {"experts": s["experts"], "top": s["top"], "scale": 1.5}, "shared": {"ff": s["shared_ff"]}}
+    return {"architecture": "Viladra", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5}, "canon": {"taps": s["taps"]},
+            "embedding": {"scale": 1.0}, "logit_softcap": 30.0, "layers": [{**mixers[c], "mlp": mlp} for c in s["order"]]}
+
+
+def build_viladra(s: dict, dev):
+    from mistral_inference_b200.args import LayeredArgs
+    from mistral_inference_b200.layered import LayeredTransformer
+    from mistral_inference_b200.transformer_layers import GlaMixer
+
+    m = LayeredTransformer.empty(LayeredArgs.from_dict(viladra_config(s)), dev, torch.bfloat16)
+    for blk in m.layers:  # the rank of the decay projection comes with a checkpoint; here it is the size table's
+        if isinstance(blk.mix, GlaMixer):
+            blk.mix.prepare("a1", (s["rank"], s["width"]))
+            blk.mix.prepare("a2", (blk.mix.nqk, s["rank"]))
+    g = torch.Generator(device=dev).manual_seed(0)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            last = n.rsplit(".", 1)[-1]
+            if last == "dwa":
+                p.fill_(1.0 / p.numel())
+            elif last == "weight" and p.dim() == 2:  # convolution taps
+                p.copy_(torch.randn(p.shape, generator=g, device=dev, dtype=torch.float32) * 0.2)
+            elif p.dim() >= 2:
+                p.copy_(torch.randn(p.shape, generator=g, device=dev, dtype=torch.float32) / math.sqrt(p.shape[-1]))
+            elif last in ("weight", "norm", "q_norm", "k_norm"):
+                p.fill_(1.0)
+            elif last == "ba2":
+                p.fill_(3.0)
+            else:
+                p.copy_(torch.randn(p.shape, generator=g, device=dev, dtype=torch.float32) * 0.1)
+    return m.eval()
+
+
+def lotazen_like(s: dict) -> dict:
+    """The closest existing design at equal size: rotary window attention beside a gated recurrence where Viladra has sigmoid-weight
+    window attention, a matrix memory where it has retention or gated linear attention, the same experts (gated there)."""
+    return dict(width=s["width"], heads=s["heads"], kv_heads=s["kv_heads"], dim=s["dim"], window=s["window"], rec_heads=s["rec_heads"], experts=s["experts"],
+                top=s["top"], ff=s["ff"], shared_ff=s["shared_ff"], vocab=s["vocab"], order="".join("p" if c == "a" else "m" for c in s["order"]),
+                lin_heads=s["rec_heads"])
+
+
+def viladra_kernel_table(s: dict, T: int, ctx: int, peaks: dict, dev) -> dict:
+    """Every kernel the design added or extended, alone at this size, each next to the like kernel of the closest design at the same shape."""
+    from mistral_inference_b200 import _abi_hybrid as h
+    from mistral_inference_b200.cache import BufferCache, LayerCacheSpec
+
+    bf = torch.bfloat16
+    W, H, G, d, win, RH, E, ff, top, taps, rank = (s[k] for k in ("width", "heads", "kv_heads", "dim", "window", "rec_heads", "experts", "ff", "top", "taps", "rank"))
+    flush = torch.zeros(160 << 20, dtype=torch.float32, device=dev)
+    rows = {}
+
+    def rec(name, ms, flops=0.0, bytes_=0.0, note=None):
+        r = {"ms": round(ms, 4)}
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 2)
+            r["of_bf16_peak"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)
+        if bytes_:
+            r["gb_s"] = round(bytes_ / ms / 1e6, 1)
+            r["of_hbm_peak"] = round(bytes_ / ms / 1e6 / peaks["hbm_gbs"], 3)
+        if note:
+            r["note"] = note
+        rows[name] = r
+
+    B = 8
+    ring = BufferCache(1, B, ctx + 8, 0, 0, None, layer_specs=[LayerCacheSpec(kind="ring", n_kv_heads=G, k_dim=d, v_dim=d, window=win)]).to(dev, bf)
+    ring.cache_k[0].normal_(); ring.cache_v[0].normal_()
+    md = ring.get_input_metadata([T])[0]
+    zero = torch.zeros(1, dtype=torch.int32, device=dev)
+    # ---- the stream: convolution in, norm and depth average out
+    x32 = torch.randn(T, W, device=dev)
+    cw = (torch.randn(W, taps, device=dev) * 0.2).to(bf)
+    cstate = torch.zeros(B, 2, taps - 1, W, device=dev)
+    nw = torch.ones(W, device=dev).to(bf)
+    rec("canon_conv prompt", _time(lambda: h.canon_conv(x32, cw, cstate, 0, md.q_start, zero, md.slots, 1, False), 3, 8, flush), bytes_=T * W * (4 + 2.0),
+        note="reads the fp32 stream, writes bf16; includes the state write-back launch")
+    rec("like: rmsnorm prompt", _time(lambda: h.rmsnorm(x32, nw, 1e-5), 3, 8, flush), bytes_=T * W * (4 + 2.0))
+    n_mix = 5
+    stack = torch.randn(n_mix + 1, T, W, device=dev)
+    y32 = torch.randn(T, W, device=dev)
+    coef = torch.full((n_mix,), 1.0 / n_mix, device=dev).to(bf)
+    rec("rmsnorm_add prompt", _time(lambda: h.rmsnorm_add(y32, nw, stack[n_mix - 1], 1e-5), 3, 8, flush), bytes_=T * W * 12.0)
+    rec(f"rmsnorm_add + depth average over {n_mix} prompt", _time(lambda: h.rmsnorm_add(y32, nw, stack[n_mix - 1], 1e-5, stack, n_mix, coef, stack[n_mix]), 3, 8, flush),
+        bytes_=T * W * 4.0 * (3 + n_mix))
+    rec("like: layernorm add prompt", _time(lambda: h.layernorm(y32, nw, nw, 1e-5, add_to=stack[0]), 3, 8, flush), bytes_=T * W * 12.0)
+    # ---- attention
+    qkv = torch.randn(T, (H + 2 * G) * d, device=dev).to(bf)
+    qn, kn = torch.ones(H * d, device=dev).to(bf), torch.ones(G * d, device=dev).to(bf)
+    rec("whole_norm_prep prompt", _time(lambda: h.whole_norm_prep(qkv, qn, kn, None, None, None, H * d, G * d, G * d, 1e-5, own=True), 3, 8, flush),
+        bytes_=2.0 * qkv.numel() * 2)
+    freq = (torch.tensor(500000.0, dtype=torch.float64) ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)).to(dev)
+    rec("like: rot_prep prompt", _time(lambda: h.rot_prep(qkv, freq, md.positions, None, None, None, H, G, d, d, d, True, 1e-5, own=True), 3, 8, flush),
+        bytes_=2.0 * qkv.numel() * 2)
+    q, k, v = h.whole_norm_prep(qkv, qn, kn, None, None, None, H * d, G * d, G * d, 1e-5, own=True)
+    o = torch.empty(T, H * d, device=dev, dtype=bf)
+    nt = (T + 63) // 64
+    pairs = sum(min(p + 1, win) for p in range(T))
+    pb = torch.zeros(H, device=dev)
+    for label, hb in (("attn_window prompt, sigmoid weights", pb), ("like: attn_window prompt, softmax", None)):
+        rec(f"{label} (tensor-core kernel, window {win})",
+            _time(lambda: h.attn_window(q, ring.cache_k[0], ring.cache_v[0], md.positions, md.q_start, md.slots, o, 1, md.window, H, G, d, d, 0.09, win, own_k=k,
+                                        own_v=v, seqpos=md.seqpos, n_tiles=nt, head_bias=hb), 2, 5, flush), flops=4.0 * d * H * pairs)
+    ring.reset(); ring.init_kvseqlens(B); ring.update_seqlens([ctx] * B)
+    md2 = ring.get_input_metadata([1] * B)[0]
+    q2, o2 = q[:B].contiguous(), torch.empty(B, H * d, device=dev, dtype=bf)
+    sp, ch = h.window_decode_plan(B, H, md2.window)
+    for label, hb in (("attn_window decode, sigmoid weights", pb), ("like: attn_window decode, softmax", None)):
+        rec(f"{label} B={B} (ring of {md2.window})",
+            _time(lambda: h.attn_window(q2, ring.cache_k[0], ring.cache_v[0], md2.positions, md2.q_start, md2.slots, o2, B, md2.window, H, G, d, d, 0.09, win,
+                                        splits=sp, chunk=ch, head_bias=hb), 3, 8, flush), bytes_=2.0 * B * min(ctx + 1, win) * G * d * 2)
+    # ---- recurrences
+    Hd = RH * d
+    qkvg = (torch.randn(T, 4 * Hd, device=dev) * 0.1).to(bf)
+    decay = torch.full((RH,), 0.97, device=dev)
+    rec("retention_qab prompt", _time(lambda: h.retention_qab(qkvg, freq, decay, md.positions, RH, d, d, d ** -0.5), 3, 8, flush), bytes_=T * Hd * (2 * 2 + 3 * 4.0))
+    z32 = torch.randn(T, Hd, device=dev)
+    rec("gla_qab prompt", _time(lambda: h.gla_qab(qkvg, z32, Hd, d ** -0.5, 1 / 16.0), 3, 8, flush), bytes_=T * Hd * (2 * 2 + 4 + 3 * 4.0))
+    lower = (torch.rand(Hd, device=dev) * 0.9).to(bf)
+    rec("like: hgrn2_gates prompt", _time(lambda: h.hgrn2_gates(qkvg, lower, Hd), 3, 8, flush), bytes_=T * Hd * (2 * 2 + 3 * 4.0))
+    qab = h.gla_qab(qkvg, z32, Hd, d ** -0.5, 1 / 16.0)
+    state = torch.zeros(B, RH, d, d, device=dev)
+    rec("gated_scan prompt (gated linear attention), chunk-parallel",
+        _time(lambda: h.gated_scan(qab, qkvg, 4 * Hd, 2 * Hd, state, md.q_start, zero, md.slots, 1, RH, d, d, ones=False, max_seqlen=T), 2, 5, flush),
+        flops=4.0 * T * RH * d * d, note="the kernel of the closest design's recurrences, same launch; useful FLOPs, the chunks run twice, fp32 FMA")
+    o32 = h.gated_scan(qab, qkvg, 4 * Hd, 2 * Hd, state, md.q_start, zero, md.slots, 1, RH, d, d, ones=False, max_seqlen=T)
+    hw = torch.ones(d, device=dev).to(bf)
+    rec("scan_post prompt (shared weight, SiLU gate)", _time(lambda: h.scan_post(o32, None, hw, False, qkvg, 4 * Hd, 3 * Hd, RH, d, False, 1e-5, silu_gate=True), 3, 8, flush),
+        bytes_=T * Hd * (4 + 2 + 2.0))
+    rec("scan_post prompt (no weight, SiLU gate)", _time(lambda: h.scan_post(o32, None, None, False, qkvg, 4 * Hd, 3 * Hd, RH, d, False, 1e-5, silu_gate=True), 3, 8, flush),
+        bytes_=T * Hd * (4 + 2 + 2.0))
+    rec("like: scan_post prompt (shared weight, no gate)", _time(lambda: h.scan_post(o32, None, hw, False, None, 0, 0, RH, d, False, 1e-5), 3, 8, flush), bytes_=T * Hd * (4 + 2.0))
+    one = torch.ones(B, dtype=torch.int32, device=dev)
+    qabB = qab[:B].contiguous()
+    rec(f"gated_scan decode B={B}", _time(lambda: h.gated_scan(qabB, qkvg, 4 * Hd, 2 * Hd, state, md2.q_start, one, md2.slots, B, RH, d, d, ones=False), 3, 8, flush),
+        bytes_=2.0 * state.numel() * 4, note="the closest design's kernel")
+    # ---- experts
+    x = torch.randn(T, W, device=dev).to(bf)
+    wr = (torch.randn(E, W, device=dev) / math.sqrt(W) * 4).to(bf)
+    rec("moe_route prompt (softmax, scaled weights)", _time(lambda: h.moe_route(x, wr, None, 1, 1, top, score=0, scale=1.5), 3, 8, flush), bytes_=T * W * 2.0)
+    rec("like: moe_route prompt (sigmoid)", _time(lambda: h.moe_route(x, wr, None, 1, 1, top, score=1), 3, 8, flush), bytes_=T * W * 2.0)
+    dense, idx, wsel = h.moe_route(x, wr, None, 1, 1, top, score=0, scale=1.5)
+    w_up = (torch.randn(E * ff, W, device=dev) * 0.02).to(bf)
+    w13 = (torch.randn(E * 2 * ff, W, device=dev) * 0.02).to(bf)
+    w2 = (torch.randn(W, E * ff, device=dev) * 0.02).to(bf)
+    xr = torch.zeros(T, W, device=dev)
+
+    def dense_form():
+        return h.linear(h.linear_relu2(x, w_up, rowscale=dense, group=ff), w2, epi=h.EPI_F32)
+
+    def dense_like():
+        return h.linear(h.linear_glu(x, w13, 7.0, 1.702, rowscale=dense, group=ff), w2, epi=h.EPI_RESIDUAL, residual=xr)
+
+    rec("experts prompt (all experts, ungated, masked)", _time(dense_form, 2, 5, flush), flops=4.0 * T * top * ff * W,
+        note=f"useful FLOPs (top {top} of {E}); the kernels compute all {E} experts")
+    rec("like: experts prompt of the scaled-input gated mixture", _time(dense_like, 2, 5, flush), flops=6.0 * T * top * ff * W)
+    for M in (1, B):
+        xs, ii, ww = x[:M].contiguous(), idx[:M].contiguous(), wsel[:M].contiguous()
+        rec(f"experts decode (chosen only, ungated) M={M}", _time(lambda: h.moe_sparse(xs, w_up, w2, ii, ww, E, ff, glu=2), 3, 8, flush),
+            bytes_=M * top * 2.0 * ff * W * 2)
+        rec(f"like: experts decode of the scaled-input gated mixture M={M}", _time(lambda: h.moe_sparse(xs, w13, w2, ii, ww, E, ff, glu=1, limit=7.0, alpha=1.702), 3, 8, flush),
+            bytes_=M * top * 3.0 * ff * W * 2)
+    # ---- one decode step's convolution and norms
+    xB = x32[:B].contiguous()
+    rec(f"canon_conv decode B={B}", _time(lambda: h.canon_conv(xB, cw, cstate, 0, md2.q_start, one, md2.slots, B, True), 3, 8, flush),
+        bytes_=B * W * (4 + 2 + 2 * (taps - 1) * 4.0), note="latency: a few KB")
+    rec(f"like: rmsnorm decode B={B}", _time(lambda: h.rmsnorm(xB, nw, 1e-5), 3, 8, flush), bytes_=B * W * (4 + 2.0))
+    return rows
+
+
+def run_viladra(a, peaks: dict) -> dict:
+    dev = torch.device("cuda", torch.cuda.current_device())
+    T, ctx = a.prefill, a.prefill
+    res = {"design": "Viladra", "dtype": "bf16", "data": "synthetic", "prompt_tokens": T, "peaks": {k: peaks.get(k) for k in ("hbm_gbs", "bf16_tflops")}, "sizes": {}}
+    for name, s in VILADRA_SIZES.items():
+        t0 = time.time()
+        m = build_viladra(s, dev)
+        new = end_to_end(m, s["vocab"], T, ctx, (1, 8), a.warmup, a.steps, dev)
+        del m
+        torch.cuda.empty_cache()
+        d = build_lotazen(lotazen_like(s), dev)
+        old = end_to_end(d, s["vocab"], T, ctx, (1, 8), a.warmup, a.steps, dev)
+        del d
+        torch.cuda.empty_cache()
+        res["sizes"][name] = {"config": s, "layered": new, "lotazen_equal_size": old, "kernels": viladra_kernel_table(s, T, ctx, peaks, dev),
+                              "seconds": round(time.time() - t0, 1)}
+    return res
+
 
 def run(a, peaks: dict) -> dict:
+    if a.design == "viladra":
+        return run_viladra(a, peaks)
     if a.design == "taruvik":
         return run_taruvik(a, peaks)
     if a.design == "lotazen":

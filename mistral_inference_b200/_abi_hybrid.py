@@ -480,13 +480,14 @@ def linear_glu(x: torch.Tensor, w: torch.Tensor, limit: float, alpha: float, row
 
 
 # ------------------------------------------------------------------------------------------------ sublayers that read the stream itself
-def canon_conv(x32: torch.Tensor, w: torch.Tensor, state: torch.Tensor, state_off: int, q_start, seqpos, slots, B: int, one_each: bool) -> torch.Tensor:
+def canon_conv(x32: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], state_off: int, q_start, seqpos, slots, B: int, one_each: bool) -> torch.Tensor:
     """h = x32 + causal convolution over time of x32 on every channel (w [D, taps]), in the weights' dtype; the sequences' last taps - 1
     inputs live in `state` (fp32 [rows, ...], this convolution's part at `state_off` floats into a row) and are advanced."""
     T, D = x32.shape
-    assert x32.dtype == torch.float32 and state.dtype == torch.float32 and w.shape[0] == D
+    assert x32.dtype == torch.float32 and w.shape[0] == D
+    assert (state is None and w.shape[1] == 1) or state.dtype == torch.float32, "more than one tap needs the state of the last inputs"
     h = torch.empty(T, D, dtype=w.dtype, device=x32.device)
-    _check(lib().mbh_canon_conv(_ptr(x32), _ptr(w), _ptr(state), state[0].numel(), state_off, _ptr(q_start), _ptr(seqpos), _ptr(slots), _ptr(h), T, B, D,
+    _check(lib().mbh_canon_conv(_ptr(x32), _ptr(w), _ptr(state), state[0].numel() if state is not None else 0, state_off, _ptr(q_start), _ptr(seqpos), _ptr(slots), _ptr(h), T, B, D,
                                 w.shape[1], int(one_each), dt_of(w.dtype), _stream()), "mbh_canon_conv")
     return h
 
