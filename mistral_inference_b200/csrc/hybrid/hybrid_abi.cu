@@ -532,7 +532,17 @@ int mbh_canon_conv(const void* x32, const void* w, void* state, int64_t state_st
     if (one_each) {
         DISPATCH(dt, canon_conv_step_kernel<ST><<<dim3((unsigned)B, cb), 256, 0, st>>>(a));
     } else {
-        DISPATCH(dt, canon_conv_kernel<ST><<<dim3((unsigned)T, cb), 256, 0, st>>>(a));
+        // the tiled kernel for the usual few taps and channel counts it can load four at a time; the plain one for everything else
+        const bool tiled = taps <= 8 && D % 4 == 0 && (reinterpret_cast<uintptr_t>(x32) | reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(state)) % 16 == 0
+                           && (state_stride % 4 == 0) && (state_off % 4 == 0);
+        if (tiled) {
+            const dim3 grid((unsigned)((T + CANON_TILE - 1) / CANON_TILE), (unsigned)((D / 4 + 127) / 128));
+#define MBH_CANON(TP) case TP: DISPATCH(dt, canon_conv_tiled_kernel<ST, TP><<<grid, 128, 0, st>>>(a, (int)T)); break;
+            switch ((int)taps) { MBH_CANON(1) MBH_CANON(2) MBH_CANON(3) MBH_CANON(4) MBH_CANON(5) MBH_CANON(6) MBH_CANON(7) MBH_CANON(8) }
+#undef MBH_CANON
+        } else {
+            DISPATCH(dt, canon_conv_kernel<ST><<<dim3((unsigned)T, cb), 256, 0, st>>>(a));
+        }
         if (taps > 1) canon_state_kernel<<<dim3((unsigned)B, cb), 256, 0, st>>>(a);
     }
     cudaError_t e = cudaGetLastError();

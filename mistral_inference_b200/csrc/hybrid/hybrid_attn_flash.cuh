@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(128) attn_bias_flash_kernel(AttnArgs a) {
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) s[nt][c] = s[nt][c] == -INFINITY ? 0.f : sigmoid_exact(s[nt][c]);
+                for (int c = 0; c < 4; ++c) s[nt][c] = s[nt][c] == -INFINITY ? 0.f : __fdividef(1.f, 1.f + __expf(-s[nt][c]));  // rounded to bf16 just below
         }
         const float mn0 = a.sigmoid ? 0.f : fmaxf(m0, quad_max(mx0)), mn1 = a.sigmoid ? 0.f : fmaxf(m1, quad_max(mx1));
         const float c0 = (a.sigmoid || mn0 == -INFINITY) ? 1.f : expf(m0 - mn0), c1 = (a.sigmoid || mn1 == -INFINITY) ? 1.f : expf(m1 - mn1);

@@ -52,6 +52,71 @@ __global__ void canon_conv_kernel(CanonArgs a) {
     }
 }
 
+// Prompts: a CTA takes CANON_TILE consecutive tokens and 4 * blockDim channels; a thread owns 4 adjacent channels (one 16-byte load
+// of the stream per token) and walks the tile's tokens with the last TAPS - 1 inputs in registers, so the stream is read once (plus
+// TAPS - 1 rows where a tile or a sequence starts).  Needs D % 4 == 0.  grid (ceil(T / CANON_TILE), ceil(D / (4 * blockDim)))
+constexpr int CANON_TILE = 16;
+
+template <typename T> __device__ __forceinline__ void store4(T* p, const float* v);
+template <> __device__ __forceinline__ void store4<float>(float* p, const float* v) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, const float* v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&lo); u.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(128) canon_conv_tiled_kernel(CanonArgs a, int T_total) {
+    constexpr int BACK = TAPS - 1;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (c >= a.D) return;
+    const int t0 = blockIdx.x * CANON_TILE, t1 = min(t0 + CANON_TILE, T_total);
+    float w[4][TAPS];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) w[u][j] = to_f(static_cast<const T*>(a.w)[(size_t)(c + u) * TAPS + j]);
+    float4 win[BACK > 0 ? BACK : 1];
+    int b = 0;
+    while (b + 1 < a.B && a.q_start[b + 1] <= t0) ++b;
+    int seq_end = a.q_start[b + 1];
+    bool fresh = true;  // the window must be (re)loaded: first token of the tile, or of a sequence
+    for (int t = t0; t < t1; ++t) {
+        if (t >= seq_end) {
+            while (b + 1 < a.B && a.q_start[b + 1] <= t) ++b;
+            seq_end = a.q_start[b + 1];
+            fresh = true;
+        }
+        if (fresh) {
+            const int i = t - a.q_start[b];
+            const bool has_state = a.seqpos[b] > 0;
+            const float* st = a.state + (size_t)a.slots[b] * a.state_stride + a.state_off;
+#pragma unroll
+            for (int j = 0; j < BACK; ++j) {
+                const int src = i - BACK + j;
+                if (src >= 0) win[j] = *reinterpret_cast<const float4*>(a.x + (size_t)(a.q_start[b] + src) * a.D + c);
+                else if (has_state) win[j] = *reinterpret_cast<const float4*>(st + (size_t)(BACK + src) * a.D + c);
+                else win[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            fresh = false;
+        }
+        const float4 xc = *reinterpret_cast<const float4*>(a.x + (size_t)t * a.D + c);
+        float o[4] = {xc.x, xc.y, xc.z, xc.w};
+#pragma unroll
+        for (int j = 0; j < BACK; ++j) {
+            o[0] = fmaf(w[0][j], win[j].x, o[0]); o[1] = fmaf(w[1][j], win[j].y, o[1]);
+            o[2] = fmaf(w[2][j], win[j].z, o[2]); o[3] = fmaf(w[3][j], win[j].w, o[3]);
+        }
+        o[0] = fmaf(w[0][BACK], xc.x, o[0]); o[1] = fmaf(w[1][BACK], xc.y, o[1]);
+        o[2] = fmaf(w[2][BACK], xc.z, o[2]); o[3] = fmaf(w[3][BACK], xc.w, o[3]);
+        store4<T>(static_cast<T*>(a.h) + (size_t)t * a.D + c, o);
+#pragma unroll
+        for (int j = 0; j + 1 < BACK; ++j) win[j] = win[j + 1];
+        if (BACK > 0) win[BACK - 1] = xc;
+    }
+}
+
 // grid (B, blocks of channels); a thread moves one channel's entries in rising order, reading only entries it has not yet written
 __global__ void canon_state_kernel(CanonArgs a) {
     const int b = blockIdx.x, back = a.taps - 1;

@@ -97,13 +97,15 @@ def _i32(xs):
 
 # ----------------------------------------------------------------------------- mechanisms alone
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("taps", [1, 2, 3, 6])
-def test_convolution_on_the_stream(dtype, taps):
+@pytest.mark.parametrize("taps", [1, 2, 3, 6, 9])
+@pytest.mark.parametrize("D", [37, 40, 520])
+def test_convolution_on_the_stream(dtype, taps, D):
     """Two sequences in rows 4 and 1 of the state, fed whole, in portions (shorter and longer than the taps reach back) and token
-    by token; a row that held another sequence before is started afresh."""
+    by token; a row that held another sequence before is started afresh.  Channel counts that the four-at-a-time prompt kernel takes
+    (40; 520: more than one CTA of channels) and one it does not; tap counts on both sides of its limit."""
     from mistral_inference_b200 import _abi_hybrid as h
 
-    D, lens = 37, (23, 9)
+    lens = (23, 9)
     g = torch.Generator().manual_seed(taps)
     xs = [torch.randn(n, D, generator=g) for n in lens]
     w = (0.5 * torch.randn(D, taps, generator=g)).to(dtype)
