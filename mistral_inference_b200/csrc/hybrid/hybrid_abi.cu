@@ -555,7 +555,9 @@ int mbh_rmsnorm_add(const void* y32, const void* w, void* acc32, int64_t T, int6
     if (stack && (!coef || !out32 || n < 1)) return bad("mbh_rmsnorm_add: the depth average needs coefficients and an output");
     NormAddArgs a{(const float*)y32, w, (float*)acc32, (int)D, eps, (const float*)stack, (size_t)stack_stride, coef, (int)n, (float*)out32};
     cudaStream_t st = (cudaStream_t)stream;
-    DISPATCH(dt, rmsnorm_add_kernel<ST><<<(unsigned)T, D >= 1024 ? 256 : 128, 0, st>>>(a));
+    const int threads = D >= 1024 ? 256 : 128;
+    const unsigned cb = T <= 32 ? (unsigned)((D + 2 * threads - 1) / (2 * threads)) : 1u;  // few rows: two columns per thread, many CTAs
+    DISPATCH(dt, rmsnorm_add_kernel<ST><<<dim3((unsigned)T, cb), threads, 0, st>>>(a));
     cudaError_t e = cudaGetLastError();
     return e ? fail(e, "mbh_rmsnorm_add") : 0;
 }

@@ -167,7 +167,8 @@ struct NormAddArgs {
     float* out;            // [T, D]
 };
 
-// one row per CTA
+// grid (rows, column blocks): with one column block a CTA takes a whole row; a decode step's few rows are spread over several CTAs,
+// each of which sums the squares of the whole row (a few KB from L2) and then updates its own slice of the columns
 template <typename T>
 __global__ void rmsnorm_add_kernel(NormAddArgs a) {
     __shared__ float red[32];
@@ -179,7 +180,8 @@ __global__ void rmsnorm_add_kernel(NormAddArgs a) {
     const float inv = 1.f / sqrtf(ss / (float)a.D + a.eps);
     const T* w = static_cast<const T*>(a.w);
     const T* cf = static_cast<const T*>(a.coef);
-    for (int i = threadIdx.x; i < a.D; i += blockDim.x) {
+    const int per = (a.D + gridDim.y - 1) / gridDim.y, c0 = blockIdx.y * per, c1 = min(a.D, c0 + per);
+    for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) {
         const float v = a.acc[row + i] + r[i] * inv * to_f(w[i]);
         a.acc[row + i] = v;
         if (a.stack) {
