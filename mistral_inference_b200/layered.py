@@ -1,11 +1,13 @@
 """Layered decoder: a model given as a list of layers, each with its own kind of token mixer (softmax attention with a
 distance bias, lightning attention with a recurrent state, latent attention, ...) and an optional feed-forward (gated, or a
 mixture of experts), optionally with a span of layers that runs several times (args.LayeredArgs; architectures "Fesenex",
-"Taruvik").  It plugs into the same places as `Transformer`: `from_folder`, `forward(input_ids, seqlens, cache)` over ragged
+"Taruvik", "Lotazen", "Viladra").  It plugs into the same places as `Transformer`: `from_folder`, `forward(input_ids, seqlens, cache)` over ragged
 batches, `BufferCache` (per-layer rings and states, `make_cache`), `forward_logprobs` / `next_token_logits` for `generate()`.
 
 On disk: config.json + model.safetensors with tensors `embed`, `l<i>.norm1|norm2` (and `norm1b|norm2b` with norms after the
-sublayers; a layer norm's bias is the weight's name + `.b`), `l<i>.mix.*`, `l<i>.mlp.*`, `final.norm`, `head`.  The residual stream is fp32; weights and activations are bf16 or fp32 (`dtype`), the latter in true
+sublayers; a layer norm's bias is the weight's name + `.b`), `l<i>.mix.*`, `l<i>.mlp.*`, `final.norm`, `head` (none when the head is
+the embedding table), and for designs that have them `l<i>.canon1|canon2` (convolution taps) and `l<i>.dwa` (depth-average weights).
+The residual stream is fp32; weights and activations are bf16 or fp32 (`dtype`), the latter in true
 fp32 arithmetic.  All compute runs in libmb200_hybrid.so (include/mistral_b200_hybrid.h); CUDA only, no fallback.
 """
 import json
