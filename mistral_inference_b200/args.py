@@ -446,7 +446,9 @@ class LayeredArgs:
                 raise ValueError(f"unknown mixer type {L['type']!r}")
             mlp = None
             if L.get("mlp") is not None:
-                kind = L["mlp"].get("kind", "dense")
+                # without "kind": the design's own feed-forward when it has exactly one, else the dense one
+                own = DESIGN_MLP_ARGS.get(d["architecture"], {})
+                kind = L["mlp"].get("kind", next(iter(own)) if len(own) == 1 else "dense")
                 if kind not in mlp_args:
                     raise ValueError(f"unknown feed-forward kind {kind!r}")
                 mlp = mlp_args[kind].from_dict(L["mlp"])

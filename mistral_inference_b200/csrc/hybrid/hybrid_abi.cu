@@ -523,7 +523,7 @@ int mbh_scan_post(const void* o32, const void* nq, int64_t d, const void* gates,
 int mbh_canon_conv(const void* x32, const void* w, void* state, int64_t state_stride, int64_t state_off, const void* q_start, const void* seqpos,
                    const void* slots, void* h, int64_t T, int64_t B, int64_t D, int64_t taps, int one_each, int dt, void* stream) {
     if (T == 0) return 0;
-    if (taps < 1 || taps > CANON_MAX_TAPS) return bad("mbh_canon_conv: 1 to 16 taps");
+    if (taps < 1) return bad("mbh_canon_conv: at least one tap");
     if (one_each && T != B) return bad("mbh_canon_conv: one token per sequence means T == B");
     CanonArgs a{(const float*)x32, w, (float*)state, (int)state_stride, (int)state_off, (const int*)q_start, (const int*)seqpos, (const int*)slots, h,
                 (int)B, (int)D, (int)taps};

@@ -26,8 +26,6 @@ struct CanonArgs {
     int B, D, taps;
 };
 
-constexpr int CANON_MAX_TAPS = 16;
-
 // grid (T, blocks of channels)
 template <typename T>
 __global__ void canon_conv_kernel(CanonArgs a) {

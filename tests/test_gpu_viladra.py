@@ -97,7 +97,7 @@ def _i32(xs):
 
 # ----------------------------------------------------------------------------- mechanisms alone
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("taps", [1, 2, 3, 6, 9])
+@pytest.mark.parametrize("taps", [1, 2, 3, 6, 9, 20])
 @pytest.mark.parametrize("D", [37, 40, 520])
 def test_convolution_on_the_stream(dtype, taps, D):
     """Two sequences in rows 4 and 1 of the state, fed whole, in portions (shorter and longer than the taps reach back) and token
